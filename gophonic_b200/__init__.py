@@ -1,0 +1,11 @@
+"""gophonic_b200: a small library that runs the Qwen3 dense decoder on one NVIDIA B200.
+
+Importing the package needs no GPU.  The kernel library is compiled and loaded the first time a
+model is opened on a CUDA device.
+"""
+from . import registry
+from .config import ConfigError, Qwen3Config
+
+__version__ = "0.1.0"
+
+__all__ = ["ConfigError", "Qwen3Config", "registry"]

@@ -1,0 +1,71 @@
+// Shared helpers of the sm_100a kernel library.
+//
+// Every exported function has C linkage, takes raw device pointers plus a cudaStream_t, launches
+// on that stream and returns 0 or a negative status; the text of the last refusal is kept per
+// thread and read with gb_last_error().  Sizes a kernel cannot take are refused on the host
+// before anything is launched, never computed wrongly.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define GB_API extern "C" __attribute__((visibility("default")))
+
+enum GbDtype : int { GB_F32 = 0, GB_BF16 = 1 };
+
+// Tokens per cache page.  Keys and values of one (page, kv head) are contiguous: [64][head_dim].
+#define GB_PAGE 64
+
+void gb_set_error(const char* fmt, ...);
+
+#define GB_REFUSE(...)            \
+    do {                          \
+        gb_set_error(__VA_ARGS__); \
+        return -1;                \
+    } while (0)
+
+#define GB_CHECK_LAUNCH(what)                                                       \
+    do {                                                                            \
+        cudaError_t e__ = cudaGetLastError();                                       \
+        if (e__ != cudaSuccess) {                                                   \
+            gb_set_error("%s: launch failed: %s", what, cudaGetErrorString(e__));   \
+            return -2;                                                              \
+        }                                                                           \
+    } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Physical location of token `pos` of the sequence whose block-table row is `bt`.
+// ring_pages > 0: the sequence keeps only that many pages and position p lives in page slot
+// (p / 64) % ring_pages (storage of a windowed group).
+__device__ __forceinline__ int64_t page_of(const int* __restrict__ bt, int pos, int ring_pages) {
+    int lp = pos / GB_PAGE;
+    if (ring_pages > 0) lp %= ring_pages;
+    return (int64_t)bt[lp];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

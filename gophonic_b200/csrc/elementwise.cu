@@ -1,0 +1,290 @@
+// Row-wise kernels: embedding gather, residual add + RMSNorm, SwiGLU, and the fused
+// per-head norm + rotary embedding + cache write.  All arithmetic is fp32; only storage varies.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+// ------------------------------------------------------------------------------------------
+// error text
+static thread_local char g_error[512];
+
+void gb_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+GB_API const char* gb_last_error() { return g_error; }
+
+GB_API int gb_abi_version() { return 1; }
+
+// ------------------------------------------------------------------------------------------
+// embedding: h[r, :] = float(table[ids[r], :])      (internal/qwen3lm/evaluator.go:594-599)
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids, int hidden,
+                                    int vocab, float* __restrict__ out) {
+    int r = blockIdx.x;
+    int id = ids[r];
+    // ids are validated on the host; an id outside the table reads row 0 rather than faulting.
+    if (id < 0 || id >= vocab) id = 0;
+    const T* src = table + (int64_t)id * hidden;
+    float* dst = out + (int64_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+GB_API int gb_embed_gather(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab,
+                           float* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0) GB_REFUSE("embed_gather: hidden %d, vocab %d", hidden, vocab);
+    if (table_dtype == GB_F32)
+        embed_gather_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, hidden, vocab, out);
+    else if (table_dtype == GB_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, hidden, vocab, out);
+    else
+        GB_REFUSE("embed_gather: unknown table dtype %d", table_dtype);
+    GB_CHECK_LAUNCH("embed_gather");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// residual add + RMSNorm                     (internal/qwen3lm/ops.go:94-108, 251-254)
+//   v = h[row] (+ delta[row]);  if the rows are not gathered, h[row] = v
+//   out[i] = v * (1 / sqrt(mean(v^2) + eps)) * w
+// One CTA of 256 threads per row; the sum of squares is taken in a fixed order (strided partial
+// sums, shuffle tree, then the 8 warp sums in order), so a row's result does not depend on what
+// else is in the batch.
+template <typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                   const float* __restrict__ w, float eps, int n, TO* __restrict__ out,
+                                   const int* __restrict__ row_index) {
+    __shared__ float warp_part[8];
+    __shared__ float inv_s;
+    int orow = blockIdx.x;
+    int row = row_index ? row_index[orow] : orow;
+    float* hr = h + (int64_t)row * n;
+    const float* dr = delta ? delta + (int64_t)row * n : nullptr;
+    bool write_back = (row_index == nullptr) && (delta != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = hr[i];
+        if (dr) v += dr[i];
+        if (write_back) hr[i] = v;
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) t += warp_part[i];
+        inv_s = 1.0f / sqrtf(t / (float)n + eps);
+    }
+    __syncthreads();
+    float inv = inv_s;
+    TO* orow_p = out + (int64_t)orow * n;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = hr[i];
+        if (dr && !write_back) v += dr[i];
+        orow_p[i] = from_f32<TO>(v * inv * w[i]);
+    }
+}
+
+GB_API int gb_add_rmsnorm(float* h, const float* delta, const float* w, float eps, int n, void* out, int out_dtype,
+                          const int* row_index, int out_rows, cudaStream_t stream) {
+    if (out_rows <= 0) return 0;
+    if (n <= 0) GB_REFUSE("add_rmsnorm: width %d", n);
+    if (out_dtype == GB_F32)
+        add_rmsnorm_kernel<float><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (float*)out, row_index);
+    else if (out_dtype == GB_BF16)
+        add_rmsnorm_kernel<__nv_bfloat16><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
+    else
+        GB_REFUSE("add_rmsnorm: unknown output dtype %d", out_dtype);
+    GB_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+// h[row] += delta[row] for all rows (the residual add after the last layer when nothing is normed).
+__global__ void add_rows_kernel(float* __restrict__ h, const float* __restrict__ delta, int64_t total) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) h[i] += delta[i];
+}
+
+GB_API int gb_add_rows(float* h, const float* delta, int rows, int n, cudaStream_t stream) {
+    int64_t total = (int64_t)rows * n;
+    if (total <= 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffff) GB_REFUSE("add_rows: %lld elements are too many for one launch", (long long)total);
+    add_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(h, delta, total);
+    GB_CHECK_LAUNCH("add_rows");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// SwiGLU: out[r, i] = silu(gu[r, i]) * gu[r, inter + i]      (internal/qwen3lm/ops.go:442-461)
+// silu is evaluated with the exponential of a non-positive argument on both branches.
+__device__ __forceinline__ float silu_f32(float x) {
+    if (x >= 0.f) return x / (1.f + expf(-x));
+    float e = expf(x);
+    return x * e / (1.f + e);
+}
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int64_t gu_stride) {
+    int r = blockIdx.y;
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const T* g = gu + (int64_t)r * gu_stride;
+    float a = to_f32<T>(g[i]);
+    float b = to_f32<T>(g[inter + i]);
+    out[(int64_t)r * inter + i] = from_f32<T>(silu_f32(a) * b);
+}
+
+GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter <= 0) GB_REFUSE("swiglu: width %d", inter);
+    if (rows > 65535) GB_REFUSE("swiglu: %d rows exceed one launch (65535); the step splits larger batches", rows);
+    dim3 grid(ceil_div(inter, 256), rows);
+    if (dtype == GB_F32)
+        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter);
+    else if (dtype == GB_BF16)
+        swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter,
+                                                               2 * (int64_t)inter);
+    else
+        GB_REFUSE("swiglu: unknown dtype %d", dtype);
+    GB_CHECK_LAUNCH("swiglu");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// per-head RMSNorm + rotate-half RoPE + cache write
+//                                  (internal/qwen3lm/ops.go:231-248, kernels_scalar.go:73-80)
+// qkv is [rows, (heads + 2 kv_heads) * d]: q heads, then k heads, then v heads.
+//   q heads: normed (if q_w) and rotated in place;
+//   k heads: normed (if k_w), rotated, stored at the row's position in the key plane;
+//   v heads: stored as they are in the value plane.
+// One warp per (row, head).  The angle table holds cos/sin of pos * theta^(-2i/rot) computed in
+// float64 on the host and rounded to fp32 (internal/qwen3lm/evaluator.go:847-858).
+struct QkRopeParams {
+    void* qkv;
+    int64_t row_stride;
+    const float* q_w;
+    const float* k_w;
+    float eps;
+    const float* cos_t;  // [capacity, rot/2] or null when rot == 0
+    const float* sin_t;
+    int rot;             // rotary width (even, <= d); 0: no rotation
+    int table_positions;
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* block_table;
+    int bt_stride;
+    int ring_pages;
+    void* k_plane;
+    void* v_plane;
+    int write_kv;
+    int rows, heads, kv_heads, d;
+};
+
+template <typename T>
+__global__ void qk_rope_kernel(QkRopeParams p) {
+    extern __shared__ float sh[];  // [4 warps][d]
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int r = blockIdx.x;
+    int head = blockIdx.y * 4 + warp;
+    int total_heads = p.heads + 2 * p.kv_heads;
+    if (head >= total_heads) return;
+    int d = p.d;
+    T* src = (T*)p.qkv + (int64_t)r * p.row_stride + (int64_t)head * d;
+    int pos = p.row_pos[r];
+    bool is_q = head < p.heads;
+    bool is_k = !is_q && head < p.heads + p.kv_heads;
+    int kvh = is_q ? 0 : (is_k ? head - p.heads : head - p.heads - p.kv_heads);
+
+    T* dst = nullptr;
+    if (is_q) {
+        dst = src;
+    } else {
+        if (!p.write_kv) return;
+        int slot = p.seq_slot[p.row_seq[r]];
+        int64_t page = page_of(p.block_table + (int64_t)slot * p.bt_stride, pos, p.ring_pages);
+        T* plane = (T*)(is_k ? p.k_plane : p.v_plane);
+        dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)d;
+    }
+    if (!is_q && !is_k) {  // value head: copy
+        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        return;
+    }
+    const float* w = is_q ? p.q_w : p.k_w;
+    float* y = sh + warp * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        float v = to_f32<T>(src[i]);
+        y[i] = v;
+        ss += v * v;
+    }
+    float inv = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)d + p.eps);
+    }
+    __syncwarp();
+    if (w)
+        for (int i = lane; i < d; i += 32) y[i] = y[i] * inv * w[i];
+    __syncwarp();
+    int half = p.rot / 2;
+    // rows whose position lies beyond the table are refused on the host
+    const float* c = p.cos_t + (int64_t)pos * half;
+    const float* s = p.sin_t + (int64_t)pos * half;
+    for (int i = lane; i < d; i += 32) {
+        float v;
+        if (i < half)
+            v = y[i] * c[i] - y[i + half] * s[i];
+        else if (i < p.rot)
+            v = y[i] * c[i - half] + y[i - half] * s[i - half];
+        else
+            v = y[i];
+        dst[i] = from_f32<T>(v);
+    }
+}
+
+GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStream_t stream) {
+    QkRopeParams p = *pp;
+    if (p.rows <= 0) return 0;
+    if (p.d <= 0 || p.d > 1024) GB_REFUSE("qk_norm_rope: head_dim %d is outside [1, 1024]", p.d);
+    if (p.rot < 0 || p.rot > p.d || (p.rot & 1)) GB_REFUSE("qk_norm_rope: rotary width %d must be even and <= head_dim %d", p.rot, p.d);
+    if (p.rot > 0 && (!p.cos_t || !p.sin_t)) GB_REFUSE("qk_norm_rope: rotary width %d without an angle table", p.rot);
+    if (p.heads <= 0 || p.kv_heads < 0) GB_REFUSE("qk_norm_rope: heads %d, kv heads %d", p.heads, p.kv_heads);
+    if (p.rows > 0x7fffffff / 2) GB_REFUSE("qk_norm_rope: %d rows are too many", p.rows);
+    int total_heads = p.heads + 2 * p.kv_heads;
+    dim3 grid(p.rows, ceil_div(total_heads, 4));
+    if (grid.y > 65535) GB_REFUSE("qk_norm_rope: %d heads exceed one launch", total_heads);
+    size_t smem = (size_t)4 * p.d * sizeof(float);
+    if (dtype == GB_F32)
+        qk_rope_kernel<float><<<grid, 128, smem, stream>>>(p);
+    else if (dtype == GB_BF16)
+        qk_rope_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(p);
+    else
+        GB_REFUSE("qk_norm_rope: unknown dtype %d", dtype);
+    GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// dtype conversion helpers used when rows are handed between precisions
+__global__ void f32_to_bf16_kernel(const float* __restrict__ a, __nv_bfloat16* __restrict__ b, int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) b[i] = __float2bfloat16_rn(a[i]);
+}
+
+GB_API int gb_f32_to_bf16(const float* a, void* b, int64_t n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffff) GB_REFUSE("f32_to_bf16: %lld elements are too many", (long long)n);
+    f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(a, (__nv_bfloat16*)b, n);
+    GB_CHECK_LAUNCH("f32_to_bf16");
+    return 0;
+}

@@ -1,0 +1,132 @@
+"""A decoder assembled from a ``ModelSpec``: embedding, blocks run in schedule order, final norm,
+head.  The class knows no architecture: everything it runs was chosen by the spec through the
+part registries.
+
+Forward pass of one step, as the reference orders it (internal/qwen3lm/evaluator.go:594-599 embed,
+638-683 layers, 685-709 final add + norm, 357-381 head): rows are packed (no padding), the
+residual is fp32, and only the rows whose logits are wanted reach the final norm and the head
+(evaluator.go:669-677 prunes to the wanted rows the same way).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from .. import registry
+from ..cache import Cache
+from ..parts.base import Runtime
+from ..weights import InitScales, declare_model, load_tensors, random_tensors_on_device
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "f32": torch.float32}
+
+
+def dtype_mode(name) -> str:
+    if isinstance(name, torch.dtype):
+        name = {torch.bfloat16: "bfloat16", torch.float32: "float32"}.get(name, str(name))
+    if name not in _DTYPES:
+        raise ValueError(f"dtype '{name}' is not one of bfloat16, float32")
+    return "bfloat16" if _DTYPES[name] == torch.bfloat16 else "float32"
+
+
+def make_runtime(mode: str, device) -> Runtime:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError(f"the engine runs on CUDA devices only (asked for '{device}'); there is no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; the engine has no CPU path")
+    from .. import ops  # builds / loads the kernel library, or raises
+    return Runtime(device=device, act_dtype=_DTYPES[mode], ops=ops)
+
+
+class Model:
+    def __init__(self, spec, tensors: Mapping[str, torch.Tensor], runtime: Runtime, config=None):
+        from .. import parts  # noqa: F401  (registers the built-in parts)
+        spec.validate()
+        self.spec = spec
+        self.config = config
+        self.rt = runtime
+        self.embedding = tensors[spec.embedding.name]
+        self.blocks = [registry.part_class("block", layer.block)(layer, layer.prefix, tensors, runtime)
+                       for layer in spec.layers]
+        norm_prefix = spec.final_norm_name[:-len("weight")]
+        self.final_norm = registry.part_class("norm", spec.final_norm.kind)(spec.final_norm, norm_prefix, tensors, runtime)
+        if spec.head.name in tensors:
+            self.head = tensors[spec.head.name]
+            self.tied = False
+        elif spec.head.tied_to is not None and spec.head.tied_to in tensors:
+            self.head = tensors[spec.head.tied_to]  # the same storage, no second copy
+            self.tied = True
+        else:
+            raise ValueError(f"no head tensor '{spec.head.name}' and nothing to tie it to")
+        if tuple(self.head.shape) != (spec.head.vocab, spec.head.hidden):
+            raise ValueError(f"head has shape {tuple(self.head.shape)}, want {(spec.head.vocab, spec.head.hidden)}")
+
+    # ---- construction --------------------------------------------------------------------
+    @classmethod
+    def from_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0") -> "Model":
+        mode = dtype_mode(dtype)
+        config = registry.read_config(model_dir)
+        spec = config.model_spec()
+        rt = make_runtime(mode, device)
+        tensors = load_tensors(model_dir, declare_model(spec), mode, rt.device)
+        return cls(spec, tensors, rt, config)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0",
+                    scales: InitScales = InitScales(), layers: Optional[int] = None) -> "Model":
+        """Random weights made on the device (for sizes too large to pass through a file)."""
+        mode = dtype_mode(dtype)
+        spec = config.model_spec()
+        rt = make_runtime(mode, device)
+        tied = bool(getattr(config, "tie_word_embeddings", False))
+        tensors = random_tensors_on_device(spec, seed, mode, rt.device, scales, tied=tied)
+        return cls(spec, tensors, rt, config)
+
+    # ---- description ---------------------------------------------------------------------
+    def cache_requests(self) -> List[Tuple[object, Optional[int]]]:
+        out = []
+        for entry in self.spec.schedule:
+            layer = self.spec.layers[entry.layer]
+            req = registry.part_class("mixer", layer.mixer.kind).cache_request(layer.mixer)
+            out.append((req, entry.cache_of))
+        return out
+
+    def new_cache(self, max_tokens: int, max_slots: Optional[int] = None,
+                  max_seq_tokens: Optional[int] = None) -> Cache:
+        cache = Cache(self.cache_requests(), max_tokens, self.rt.device, self.rt.act_dtype, max_slots, max_seq_tokens)
+        capacity = cache.max_pages_per_seq * 64
+        for b in self.blocks:
+            b.mixer.prepare(capacity)
+        return cache
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights a step reads once: every layer run's matrices and the head."""
+        total = self.head.numel() * self.head.element_size()
+        for entry in self.spec.schedule:
+            b = self.blocks[entry.layer]
+            for part in (b.mixer, b.feed_forward):
+                if hasattr(part, "weight_bytes"):
+                    total += part.weight_bytes()
+        return total
+
+    # ---- forward -------------------------------------------------------------------------
+    def forward(self, batch, cache: Cache, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Run the rows of ``batch`` through every scheduled layer; return fp32 logits
+        [len(want_rows), vocab] for the wanted packed rows (None if none are wanted)."""
+        ops = self.rt.ops
+        rows = batch.rows
+        h = torch.empty((rows, self.spec.hidden), dtype=torch.float32, device=self.rt.device)
+        ops.embed_gather(self.embedding, batch.ids, h)
+        delta = None
+        for pos, entry in enumerate(self.spec.schedule):
+            delta = self.blocks[entry.layer].forward(batch, h, delta, cache.view(pos))
+        if want_rows is None or want_rows.numel() == 0:
+            return None
+        n = want_rows.numel()
+        x = torch.empty((n, self.spec.hidden), dtype=self.rt.act_dtype, device=self.rt.device)
+        self.final_norm.forward(h, x, delta, rows=want_rows)
+        logits = torch.empty((n, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
+        ops.gemm(x, self.head, logits)
+        return logits

@@ -1,0 +1,214 @@
+"""The step function: run the tokens a step brings, as one packed batch, from the cache, and
+return logits at the wanted places.
+
+A step is a list of (slot, tokens) entries.  The sequences of a step start together (each
+brings its whole prompt, lengths unequal) or go on by one token each; the function itself takes
+any mix of lengths, so a long prompt can also be fed in pieces.  Rows are packed without
+padding; each row carries (sequence, absolute position) and attends only to keys of its own
+sequence at positions <= its own (internal/qwen3lm/evaluator.go:582-602 packs unequal sequences
+the same way, with per-row start/position; gpu_darwin.go:1578-1593).  Everything is validated
+before the cache is touched, so a refused step leaves every sequence as it was
+(internal/qwen3lm/decode_batch.go:80-128).  Very large steps are cut into row chunks
+(gpu_darwin.go:1471-1487 loops long prompts pass by pass); a chunk boundary changes no result
+beyond rounding because later rows read earlier keys from the cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import Cache, CacheError
+from .model import Model
+
+
+class StepError(ValueError):
+    pass
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of the rows of one (chunk of a) step."""
+    rows: int
+    nseq: int
+    max_q_len: int
+    max_kv_len: int
+    ids: torch.Tensor          # [rows] int32 token ids
+    row_pos: torch.Tensor      # [rows] absolute position of each row in its sequence
+    row_seq: torch.Tensor      # [rows] index of the row's sequence within this batch
+    seq_slot: torch.Tensor     # [nseq] cache slot
+    seq_q_start: torch.Tensor  # [nseq] first packed row
+    seq_q_len: torch.Tensor    # [nseq] rows in this batch
+    seq_kv_len: torch.Tensor   # [nseq] keys visible to the sequence's last row (= its length after them)
+    device: torch.device = None
+    sm_count: int = 148
+    fixed_splits: Optional[int] = None
+    _scratch: Dict[Tuple[int, int, int], torch.Tensor] = field(default_factory=dict)
+
+    def decode_splits(self, heads: int, kv_heads: int, head_dim: int) -> Tuple[int, Optional[torch.Tensor]]:
+        """How many pieces single-token attention cuts each sequence's keys into, and the scratch
+        the pieces are merged through.  Few sequences with long contexts are cut so that every SM
+        has work; many sequences are not cut."""
+        if self.fixed_splits is not None:
+            splits = self.fixed_splits
+        else:
+            splits = choose_splits(self.nseq * kv_heads, self.max_kv_len, self.sm_count)
+        if splits <= 1:
+            return 1, None
+        key = (heads, head_dim, splits)
+        if key not in self._scratch:
+            n = self.nseq * heads * splits * (head_dim + 2)
+            self._scratch[key] = torch.empty(n, dtype=torch.float32, device=self.device)
+        return splits, self._scratch[key]
+
+
+def choose_splits(units: int, max_kv_len: int, sm_count: int = 148) -> int:
+    """``units`` = (sequence, kv head) pairs, each one CTA per split."""
+    by_len = max(1, max_kv_len // 256)
+    by_occupancy = max(1, (2 * sm_count) // max(1, units))
+    return int(max(1, min(by_len, by_occupancy, 32)))
+
+
+def build_batch(pieces: Sequence[Tuple[int, Sequence[int], int]], device, sm_count: int = 148,
+                want_rows: Optional[Sequence[int]] = None) -> Tuple[StepBatch, Optional[torch.Tensor]]:
+    """``pieces[i] = (slot, tokens, first_position)``: one device upload for all row metadata."""
+    nseq = len(pieces)
+    rows = sum(len(t) for _, t, _ in pieces)
+    nw = 0 if want_rows is None else len(want_rows)
+    buf = np.empty(3 * rows + 4 * nseq + nw, dtype=np.int32)
+    ids, row_pos, row_seq = buf[:rows], buf[rows:2 * rows], buf[2 * rows:3 * rows]
+    o = 3 * rows
+    seq_slot, q_start, q_len, kv_len = (buf[o + i * nseq:o + (i + 1) * nseq] for i in range(4))
+    r = 0
+    max_q = max_kv = 0
+    for i, (slot, toks, first) in enumerate(pieces):
+        n = len(toks)
+        ids[r:r + n] = toks
+        row_pos[r:r + n] = np.arange(first, first + n, dtype=np.int32)
+        row_seq[r:r + n] = i
+        seq_slot[i], q_start[i], q_len[i], kv_len[i] = slot, r, n, first + n
+        max_q, max_kv = max(max_q, n), max(max_kv, first + n)
+        r += n
+    if nw:
+        buf[o + 4 * nseq:] = want_rows
+    dev = torch.from_numpy(buf).to(device)
+    o2 = o + 4 * nseq
+    batch = StepBatch(rows=rows, nseq=nseq, max_q_len=max_q, max_kv_len=max_kv, ids=dev[:rows],
+                      row_pos=dev[rows:2 * rows], row_seq=dev[2 * rows:3 * rows],
+                      seq_slot=dev[o:o + nseq], seq_q_start=dev[o + nseq:o + 2 * nseq],
+                      seq_q_len=dev[o + 2 * nseq:o + 3 * nseq], seq_kv_len=dev[o + 3 * nseq:o2],
+                      device=torch.device(device), sm_count=sm_count)
+    return batch, (dev[o2:] if nw else None)
+
+
+class Engine:
+    """A model, its cache and the step function over them."""
+
+    def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
+                 max_seq_tokens: Optional[int] = None, max_rows_per_pass: int = 16384):
+        self.model = model
+        self.device = model.rt.device
+        self.cache: Cache = model.new_cache(max_tokens, max_slots, max_seq_tokens)
+        self.capacity = self.cache.max_pages_per_seq * 64
+        self.max_rows_per_pass = max_rows_per_pass
+        self.vocab = model.spec.vocab
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.passes = 0
+
+    # ---- slots ---------------------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.alloc_slot()
+
+    def end_sequence(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ------------------------------------------------------------------------
+    def validate(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]]):
+        if not entries:
+            raise StepError("a step without entries")
+        if want is not None and len(want) != len(entries):
+            raise StepError(f"{len(want)} want lists for {len(entries)} entries")
+        seen = set()
+        for i, (slot, toks) in enumerate(entries):
+            if slot in seen:
+                raise StepError(f"slot {slot} appears twice in one step")
+            seen.add(slot)
+            try:
+                have = self.cache.length(slot)
+            except CacheError as e:
+                raise StepError(str(e)) from None
+            if len(toks) == 0:
+                raise StepError(f"entry {i} (slot {slot}) brings no tokens")
+            if have + len(toks) > self.capacity:
+                raise StepError(f"entry {i} (slot {slot}): {have} + {len(toks)} tokens exceed the per-sequence "
+                                f"capacity {self.capacity}")
+            for t in toks:
+                if not 0 <= int(t) < self.vocab:
+                    raise StepError(f"entry {i} (slot {slot}): token id {t} is outside [0, {self.vocab})")
+            if want is not None:
+                for w in want[i]:
+                    if not 0 <= int(w) < len(toks):
+                        raise StepError(f"entry {i} (slot {slot}): wanted place {w} is outside its {len(toks)} tokens")
+
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """Run ``entries = [(slot, tokens), ...]``; return fp32 logits [sum(len(w) for w in want), vocab]
+        in the order of the entries and of each want list.  ``want=None`` asks for the last place
+        of every entry."""
+        self.validate(entries, want)
+        if want is None:
+            want = [[len(toks) - 1] for _, toks in entries]
+        grow = [(slot, self.cache.length(slot) + len(toks)) for slot, toks in entries]
+        self.cache.reserve(grow)  # raises CacheFull without changing anything
+
+        # packed row index of every wanted place, in output order
+        starts, r = [], 0
+        for _, toks in entries:
+            starts.append(r)
+            r += len(toks)
+        total_rows = r
+        want_rows = [starts[i] + int(w) for i in range(len(entries)) for w in want[i]]
+
+        if total_rows <= self.max_rows_per_pass:
+            pieces = [(slot, list(toks), self.cache.length(slot)) for slot, toks in entries]
+            logits = self._pass(pieces, want_rows)
+        else:
+            logits = self._chunked(entries, starts, want_rows)
+        self.cache.commit(grow)
+        return logits
+
+    def _pass(self, pieces, want_rows: Sequence[int]) -> Optional[torch.Tensor]:
+        batch, want_dev = build_batch(pieces, self.device, self.sm_count, want_rows if want_rows else None)
+        self.passes += 1
+        return self.model.forward(batch, self.cache, want_dev)
+
+    def _chunked(self, entries, starts, want_rows) -> Optional[torch.Tensor]:
+        """Cut the packed rows into passes of at most ``max_rows_per_pass`` rows."""
+        order: Dict[int, List[int]] = {}
+        for k, row in enumerate(want_rows):
+            order.setdefault(row, []).append(k)
+        n_want = len(want_rows)
+        result = None
+        if n_want:
+            result = torch.empty((n_want, self.vocab), dtype=torch.float32, device=self.device)
+        lo = 0
+        total = starts[-1] + len(entries[-1][1])
+        while lo < total:
+            hi = min(total, lo + self.max_rows_per_pass)
+            pieces = []
+            for i, (slot, toks) in enumerate(entries):
+                a, b = max(lo, starts[i]), min(hi, starts[i] + len(toks))
+                if a < b:
+                    pieces.append((slot, list(toks[a - starts[i]:b - starts[i]]), self.cache.length(slot) + a - starts[i]))
+            local = sorted({row for row in want_rows if lo <= row < hi})
+            logits = self._pass(pieces, [row - lo for row in local])
+            for j, row in enumerate(local):
+                for k in order[row]:
+                    result[k].copy_(logits[j])
+            lo = hi
+        return result

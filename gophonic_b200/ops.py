@@ -1,0 +1,362 @@
+"""Python face of the sm_100a kernel library.
+
+Each function checks its tensors (device, dtype, layout, sizes), passes raw pointers and the
+current torch CUDA stream to the C entry point, and raises ``KernelError`` with the library's own
+message if the kernel refuses the call.  Nothing here computes: there is no CPU path and no
+torch fallback.  Importing this module builds the library if needed and fails if that fails.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_float, c_int, c_int64, c_uint64, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+PAGE = 64  # tokens per cache page; the kernels' GB_PAGE
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = _build.load()
+
+
+def library_file() -> str:
+    return _lib._name
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(_lib.gb_last_error().decode("utf-8", "replace"))
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dim=None, contiguous=True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is on {t.device}; kernels run on CUDA tensors only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: dtype {t.dtype}, want {dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name}: {t.dim()} dimensions, want {dim}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name}: tensor is not contiguous")
+
+
+# ---- embedding ---------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, :] = float32(table[ids[r], :])."""
+    _need(table, "embed table", dim=2)
+    _need(ids, "ids", torch.int32, 1)
+    _need(out, "embed out", torch.float32, 2)
+    rows, hidden = out.shape
+    if ids.numel() != rows or table.shape[1] != hidden:
+        raise KernelError(f"embed_gather: {ids.numel()} ids, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_embed_gather(_ptr(table), _code(table.dtype), _ptr(ids), c_int(rows), c_int(hidden),
+                                c_int(table.shape[0]), _ptr(out), _stream()))
+
+
+# ---- norm --------------------------------------------------------------------------------
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """h += delta (if given, in place, unless ``rows`` selects); out = rmsnorm(h) * weight."""
+    _need(h, "residual", torch.float32, 2)
+    _need(weight, "norm weight", torch.float32, 1)
+    _need(out, "norm out", dim=2)
+    n = h.shape[1]
+    if weight.numel() != n or out.shape[1] != n:
+        raise KernelError(f"add_rmsnorm: residual width {n}, weight {weight.numel()}, out {tuple(out.shape)}")
+    if delta is not None:
+        _need(delta, "delta", torch.float32, 2)
+        if delta.shape != h.shape:
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} vs residual {tuple(h.shape)}")
+    if rows is not None:
+        _need(rows, "row index", torch.int32, 1)
+        out_rows = rows.numel()
+    else:
+        out_rows = h.shape[0]
+    if out.shape[0] != out_rows:
+        raise KernelError(f"add_rmsnorm: out has {out.shape[0]} rows, want {out_rows}")
+    _check(_lib.gb_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(weight), c_float(eps), c_int(n), _ptr(out),
+                               _code(out.dtype), _ptr(rows), c_int(out_rows), _stream()))
+
+
+def add_rows(h: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(h, "residual", torch.float32, 2)
+    _need(delta, "delta", torch.float32, 2)
+    if delta.shape != h.shape:
+        raise KernelError(f"add_rows: {tuple(delta.shape)} vs {tuple(h.shape)}")
+    _check(_lib.gb_add_rows(_ptr(h), _ptr(delta), c_int(h.shape[0]), c_int(h.shape[1]), _stream()))
+
+
+# ---- feed-forward activation -------------------------------------------------------------
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, i] = silu(gate_up[r, i]) * gate_up[r, I + i]."""
+    _need(gate_up, "gate_up", dim=2)
+    _need(out, "swiglu out", gate_up.dtype, 2)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2):
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_swiglu(_ptr(gate_up), _ptr(out), _code(out.dtype), c_int(rows), c_int(two_i // 2), _stream()))
+
+
+# ---- matrix products ---------------------------------------------------------------------
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T with fp32 multiply-add on the CUDA cores (any dtypes)."""
+    _need(a, "gemm a", dim=2, contiguous=False)
+    _need(w, "gemm w", dim=2)
+    _need(out, "gemm out", dim=2, contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_gemm_simt(_ptr(a), _code(a.dtype), _ptr(w), _code(w.dtype), _ptr(out), _code(out.dtype),
+                             c_int(M), c_int(N), c_int(K), c_int64(a.stride(0)), c_int64(w.stride(0)),
+                             c_int64(out.stride(0)), _stream()))
+
+
+def _has(name: str) -> bool:
+    return hasattr(_lib, name)
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto") -> str:
+    """out = a @ w^T, choosing the kernel by operand types and sizes.  Returns the kernel's name.
+
+    bfloat16 activations with bfloat16 weights go to the tensor-core kernels (a weight-streaming
+    kernel for up to 64 rows, tiled kernels above); everything else, and every shape those
+    kernels refuse, goes to the fp32 CUDA-core kernel.  float32 operands never touch a tensor
+    core.
+    """
+    M, K = a.shape
+    N = w.shape[0]
+    if algo == "simt" or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        gemm_simt(a, w, out)
+        return "simt"
+    aligned = (K % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+               and a.stride(1) == 1 and w.is_contiguous())
+    if not aligned:
+        gemm_simt(a, w, out)
+        return "simt"
+    if algo == "auto":
+        if M <= 64 and _has("gb_gemm_skinny"):
+            algo = "skinny"
+        elif _has("gb_gemm_tc5") and M >= 128 and tc5_accepts(a, w, out):
+            algo = "tc5"
+        elif _has("gb_gemm_mma"):
+            algo = "mma"
+        else:
+            algo = "simt"
+    if algo == "skinny":
+        _check(_lib.gb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                   c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    elif algo == "mma":
+        _check(_lib.gb_gemm_mma(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    elif algo == "tc5":
+        _check(_lib.gb_gemm_tc5(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    elif algo == "simt":
+        gemm_simt(a, w, out)
+    else:
+        raise KernelError(f"gemm: unknown algorithm '{algo}'")
+    return algo
+
+
+def tc5_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    K = a.shape[1]
+    N = w.shape[0]
+    return (K % 64 == 0 and N % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)
+
+
+# ---- attention ---------------------------------------------------------------------------
+class _QkRopeParams(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("row_stride", c_int64), ("q_w", c_void_p), ("k_w", c_void_p), ("eps", c_float),
+        ("cos_t", c_void_p), ("sin_t", c_void_p), ("rot", c_int), ("table_positions", c_int),
+        ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p), ("block_table", c_void_p),
+        ("bt_stride", c_int), ("ring_pages", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
+        ("write_kv", c_int), ("rows", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
+    ]
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                          q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                          row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
+                          block_table: torch.Tensor, ring_pages: int,
+                          k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool) -> None:
+    """Per-head RMSNorm of q and k, rotary embedding of both, q in place, k and v into the cache."""
+    _need(qkv, "qkv", dim=2)
+    rows = qkv.shape[0]
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"qk_norm_rope: qkv {tuple(qkv.shape)} for {heads}+2x{kv_heads} heads of {head_dim}")
+    for t, nm in ((q_weight, "q norm"), (k_weight, "k norm")):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.numel() != head_dim:
+                raise KernelError(f"qk_norm_rope: {nm} weight has {t.numel()} elements, head_dim is {head_dim}")
+    table_positions = 0
+    if rotary_dim > 0:
+        _need(cos, "rope cos", torch.float32, 2)
+        _need(sin, "rope sin", torch.float32, 2)
+        if cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"qk_norm_rope: angle tables {tuple(cos.shape)} for rotary width {rotary_dim}")
+        table_positions = cos.shape[0]
+    for t, nm in ((row_pos, "row_pos"), (row_seq, "row_seq"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if write_kv:
+        for t, nm in ((k_plane, "key plane"), (v_plane, "value plane")):
+            _need(t, nm, qkv.dtype, 4)
+            if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != head_dim:
+                raise KernelError(f"qk_norm_rope: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {head_dim}")
+    p = _QkRopeParams(qkv.data_ptr(), qkv.stride(0), 0 if q_weight is None else q_weight.data_ptr(),
+                      0 if k_weight is None else k_weight.data_ptr(), eps,
+                      0 if cos is None else cos.data_ptr(), 0 if sin is None else sin.data_ptr(), rotary_dim,
+                      table_positions, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
+                      block_table.data_ptr(), block_table.stride(0), ring_pages,
+                      0 if k_plane is None else k_plane.data_ptr(), 0 if v_plane is None else v_plane.data_ptr(),
+                      1 if write_kv else 0, rows, heads, kv_heads, head_dim)
+    _check(_lib.gb_qk_norm_rope_kv_write(byref(p), _code(qkv.dtype), _stream()))
+
+
+class _AttnParams(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("q_row_stride", c_int64), ("out", c_void_p), ("out_row_stride", c_int64),
+        ("k_plane", c_void_p), ("v_plane", c_void_p), ("block_table", c_void_p), ("bt_stride", c_int),
+        ("ring_pages", c_int), ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
+        ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
+        ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
+    ]
+
+
+def attention_scratch_floats(nseq: int, heads: int, head_dim: int, num_splits: int) -> int:
+    return nseq * heads * num_splits * (head_dim + 2)
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+              block_table: torch.Tensor, ring_pages: int, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+              seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
+              heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
+              num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto") -> str:
+    """Causal GQA over the paged cache.  q is a [rows, >= heads*head_dim] view (row stride free),
+    out is [rows, heads*head_dim].  Returns the kernel's name."""
+    _need(q, "attention q", dim=2, contiguous=False)
+    _need(out, "attention out", q.dtype, 2, contiguous=False)
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] < heads * head_dim or out.shape[1] < heads * head_dim:
+        raise KernelError(f"attention: q {tuple(q.shape)}, out {tuple(out.shape)} for {heads} heads of {head_dim}")
+    for t, nm in ((k_plane, "key plane"), (v_plane, "value plane")):
+        _need(t, nm, q.dtype, 4)
+        if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != head_dim:
+            raise KernelError(f"attention: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {head_dim}")
+    for t, nm in ((seq_slot, "seq_slot"), (seq_q_start, "seq_q_start"), (seq_q_len, "seq_q_len"),
+                  (seq_kv_len, "seq_kv_len")):
+        _need(t, nm, torch.int32, 1)
+        if t.numel() < nseq:
+            raise KernelError(f"attention: {nm} has {t.numel()} entries for {nseq} sequences")
+    _need(block_table, "block table", torch.int32, 2)
+    if num_splits > 1:
+        if scratch is None:
+            raise KernelError("attention: key splits need scratch memory")
+        _need(scratch, "attention scratch", torch.float32)
+        if scratch.numel() < attention_scratch_floats(nseq, heads, head_dim, num_splits):
+            raise KernelError("attention: scratch is too small")
+    p = _AttnParams(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_plane.data_ptr(), v_plane.data_ptr(),
+                    block_table.data_ptr(), block_table.stride(0), ring_pages, seq_slot.data_ptr(),
+                    seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
+                    head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr())
+    if algo == "auto":
+        algo = "simt"
+        if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256:
+            if max_q_len == 1 and _has("gb_attention_decode_mma"):
+                algo = "decode_mma"
+            elif max_q_len > 1 and _has("gb_attention_prefill_mma"):
+                algo = "prefill_mma"
+    if algo == "simt":
+        _check(_lib.gb_attention_simt(byref(p), _code(q.dtype), _stream()))
+    elif algo == "decode_mma":
+        _check(_lib.gb_attention_decode_mma(byref(p), _stream()))
+    elif algo == "prefill_mma":
+        _check(_lib.gb_attention_prefill_mma(byref(p), _stream()))
+    else:
+        raise KernelError(f"attention: unknown algorithm '{algo}'")
+    return algo
+
+
+# ---- sampling ----------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32, 2, contiguous=False)
+    _need(out, "argmax out", torch.int32, 1)
+    if logits.stride(1) != 1 or out.numel() != logits.shape[0]:
+        raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {out.numel()}")
+    _check(_lib.gb_argmax(_ptr(logits), c_int(logits.shape[0]), c_int(logits.shape[1]), c_int64(logits.stride(0)),
+                          _ptr(out), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seed: torch.Tensor, draw: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row: greedy where temperature <= 0, else top-k / top-p sampling with the
+    counter-based draw (seed[r], draw[r])."""
+    _need(logits, "logits", torch.float32, 2, contiguous=False)
+    rows = logits.shape[0]
+    _need(temperature, "temperature", torch.float32, 1)
+    _need(top_k, "top_k", torch.int32, 1)
+    _need(top_p, "top_p", torch.float32, 1)
+    _need(seed, "seed", torch.int64, 1)
+    _need(draw, "draw", torch.int64, 1)
+    _need(out, "sample out", torch.int32, 1)
+    for t in (temperature, top_k, top_p, seed, draw, out):
+        if t.numel() < rows:
+            raise KernelError("sample: a per-row option tensor is shorter than the batch")
+    if logits.stride(1) != 1:
+        raise KernelError("sample: logits rows are not contiguous")
+    _check(_lib.gb_sample(_ptr(logits), c_int(rows), c_int(logits.shape[1]), c_int64(logits.stride(0)),
+                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _ptr(out), _stream()))
+
+
+def presence_penalty(logits: torch.Tensor, seen: torch.Tensor, seen_row: torch.Tensor, presence: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32, 2, contiguous=False)
+    _need(seen, "seen bitmap", torch.int32, 2)
+    _need(seen_row, "seen row", torch.int32, 1)
+    _need(presence, "presence", torch.float32, 1)
+    rows, vocab = logits.shape
+    if seen.shape[1] * 32 < vocab:
+        raise KernelError("presence_penalty: bitmap is narrower than the vocabulary")
+    _check(_lib.gb_presence_penalty(_ptr(logits), c_int(rows), c_int(vocab), c_int64(logits.stride(0)), _ptr(seen),
+                                    c_int64(seen.stride(0)), _ptr(seen_row), _ptr(presence), _stream()))
+
+
+def mark_seen(tokens: torch.Tensor, vocab: int, seen: torch.Tensor, seen_row: torch.Tensor) -> None:
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(seen, "seen bitmap", torch.int32, 2)
+    _need(seen_row, "seen row", torch.int32, 1)
+    _check(_lib.gb_mark_seen(_ptr(tokens), c_int(tokens.numel()), c_int(vocab), _ptr(seen), c_int64(seen.stride(0)),
+                             _ptr(seen_row), _stream()))
+
+
+def f32_to_bf16(a: torch.Tensor, out: torch.Tensor) -> None:
+    _need(a, "a", torch.float32)
+    _need(out, "out", torch.bfloat16)
+    if a.numel() != out.numel():
+        raise KernelError("f32_to_bf16: sizes differ")
+    _check(_lib.gb_f32_to_bf16(_ptr(a), _ptr(out), c_int64(a.numel()), _stream()))

@@ -1,0 +1,87 @@
+"""Grouped-query causal attention over the paged cache.
+
+Per row: q, k, v = x Wq^T, x Wk^T, x Wv^T in one product (internal/qwen3lm/evaluator.go:648);
+optional per-head RMSNorm of q and k, then the position encoding, k and v stored at the row's
+position (internal/qwen3lm/ops.go:231-248; gpu.metal:1032-1055); scores (q.k) * scale over the
+keys j <= i of the same sequence, within the window if there is one; streaming softmax in fp32;
+out = ctx Wo^T (internal/qwen3lm/ops.go:259-293; evaluator.go:678).  Head h reads kv head
+h // (heads / kv_heads).
+
+The part knows sizes and constants only through its spec.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from .. import registry
+from .base import KVRequest, Mixer, Runtime, TensorDecl
+
+
+class Attention(Mixer):
+    @classmethod
+    def declare(cls, spec, prefix: str) -> List[TensorDecl]:
+        qd, kvd = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+        decls = [TensorDecl(prefix + "q_proj.weight", (qd, spec.hidden)),
+                 TensorDecl(prefix + "k_proj.weight", (kvd, spec.hidden)),
+                 TensorDecl(prefix + "v_proj.weight", (kvd, spec.hidden)),
+                 TensorDecl(prefix + "o_proj.weight", (spec.hidden, qd))]
+        if spec.qk_norm is not None:
+            decls += [TensorDecl(prefix + "q_norm.weight", (spec.head_dim,), role="norm"),
+                      TensorDecl(prefix + "k_norm.weight", (spec.head_dim,), role="norm")]
+        return decls
+
+    @classmethod
+    def cache_request(cls, spec):
+        return KVRequest(kv_heads=spec.kv_heads, head_dim=spec.head_dim, window=spec.window)
+
+    def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        if spec.heads % spec.kv_heads:
+            raise ValueError(f"{prefix}: {spec.heads} heads are not a multiple of {spec.kv_heads} kv heads")
+        self.spec = spec
+        self.rt = runtime
+        q, k, v = (tensors[prefix + n] for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight"))
+        if not (q.dtype == k.dtype == v.dtype):
+            raise ValueError(f"{prefix}: q/k/v projections are stored as {q.dtype}/{k.dtype}/{v.dtype}; they must agree")
+        self.qkv = torch.cat([q, k, v], dim=0).contiguous()
+        self.o = tensors[prefix + "o_proj.weight"].contiguous()
+        self.q_norm = self.k_norm = None
+        self.eps = 0.0
+        if spec.qk_norm is not None:
+            self.q_norm = tensors[prefix + "q_norm.weight"].to(torch.float32).contiguous()
+            self.k_norm = tensors[prefix + "k_norm.weight"].to(torch.float32).contiguous()
+            self.eps = float(spec.qk_norm.eps)
+        pos_cls = registry.part_class("position", spec.position.kind)
+        self.position = pos_cls(spec.position, prefix, tensors, runtime)
+        self.q_dim = spec.heads * spec.head_dim
+        self.kv_dim = spec.kv_heads * spec.head_dim
+
+    def weight_bytes(self) -> int:
+        return self.qkv.numel() * self.qkv.element_size() + self.o.numel() * self.o.element_size()
+
+    def prepare(self, capacity: int) -> None:
+        self.position.prepare(capacity)
+
+    def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+        ops, s = self.rt.ops, self.spec
+        rows = x.shape[0]
+        if cache is None:
+            raise ValueError("attention needs a key/value cache plane")
+        if cache.k.dtype != x.dtype:
+            raise ValueError(f"attention: cache holds {cache.k.dtype}, activations are {x.dtype}")
+        qkv = torch.empty((rows, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
+        ops.gemm(x, self.qkv, qkv)
+        cos, sin, rot = self.position.kernel_args()
+        ops.qk_norm_rope_kv_write(qkv, s.heads, s.kv_heads, s.head_dim, self.q_norm, self.k_norm, self.eps,
+                                  cos, sin, rot, batch.row_pos, batch.row_seq, batch.seq_slot,
+                                  cache.block_table, cache.ring_pages, cache.k, cache.v, cache.writable)
+        ctx = torch.empty((rows, self.q_dim), dtype=x.dtype, device=x.device)
+        splits, scratch = 1, None
+        if batch.max_q_len == 1:
+            splits, scratch = batch.decode_splits(s.heads, s.kv_heads, s.head_dim)
+        ops.attention(qkv[:, :self.q_dim], ctx, cache.k, cache.v, cache.block_table, cache.ring_pages,
+                      batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len, batch.nseq,
+                      batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),
+                      splits, scratch)
+        ops.gemm(ctx, self.o, out)

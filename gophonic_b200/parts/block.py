@@ -1,0 +1,59 @@
+"""Block arrangements: how a layer's mixer, feed-forward and norms are wired around the residual.
+
+``PreNormBlock``: h += mixer(norm_m(h)); h += ffn(norm_f(h)).  The feed-forward's output is not
+added at once: it is handed on as ``delta`` and added by whatever norms the residual next (the
+next block's first norm, or the final norm), in the same kernel that takes the statistics
+(internal/qwen3lm/evaluator.go:641-647, 678-682; ops.go:94-108 does the same).  The residual h
+stays fp32 throughout.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from .. import registry
+from .base import Part, Runtime, TensorDecl
+
+
+class PreNormBlock(Part):
+    category = "block"
+
+    @classmethod
+    def declare(cls, layer, prefix: str = "") -> List[TensorDecl]:
+        p = layer.prefix
+        decls: List[TensorDecl] = []
+        decls += registry.part_class("norm", layer.mixer_norm.kind).declare(layer.mixer_norm, p + layer.mixer_norm_prefix)
+        decls += registry.part_class("mixer", layer.mixer.kind).declare(layer.mixer, p + layer.mixer_prefix)
+        decls += registry.part_class("norm", layer.feed_forward_norm.kind).declare(
+            layer.feed_forward_norm, p + layer.feed_forward_norm_prefix)
+        decls += registry.part_class("feed_forward", layer.feed_forward.kind).declare(
+            layer.feed_forward, p + layer.feed_forward_prefix)
+        return decls
+
+    def __init__(self, layer, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        p = layer.prefix
+        self.layer = layer
+        self.rt = runtime
+        self.mixer_norm = registry.part_class("norm", layer.mixer_norm.kind)(
+            layer.mixer_norm, p + layer.mixer_norm_prefix, tensors, runtime)
+        self.mixer = registry.part_class("mixer", layer.mixer.kind)(
+            layer.mixer, p + layer.mixer_prefix, tensors, runtime)
+        self.feed_forward_norm = registry.part_class("norm", layer.feed_forward_norm.kind)(
+            layer.feed_forward_norm, p + layer.feed_forward_norm_prefix, tensors, runtime)
+        self.feed_forward = registry.part_class("feed_forward", layer.feed_forward.kind)(
+            layer.feed_forward, p + layer.feed_forward_prefix, tensors, runtime)
+
+    def forward(self, batch, h: torch.Tensor, delta: Optional[torch.Tensor], cache) -> torch.Tensor:
+        """Runs the layer on residual ``h`` (fp32, updated in place) with the pending addend
+        ``delta``; returns the new pending addend."""
+        rows, hidden = h.shape
+        act = self.rt.act_dtype
+        x = torch.empty((rows, hidden), dtype=act, device=h.device)
+        self.mixer_norm.forward(h, x, delta)
+        mixed = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
+        self.mixer.forward(batch, x, mixed, cache)
+        self.feed_forward_norm.forward(h, x, mixed)
+        out = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
+        self.feed_forward.forward(batch, x, out)
+        return out

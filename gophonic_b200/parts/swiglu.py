@@ -1,0 +1,39 @@
+"""SwiGLU feed-forward: out = down(silu(gate(x)) * up(x))  (internal/qwen3lm/evaluator.go:679-682;
+ops.go:442-461).  gate and up are kept as one [2I, H] matrix so x is read once
+(internal/qwen3lm/evaluator.go:680 projects both in one dispatch)."""
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from .base import FeedForward, Runtime, TensorDecl
+
+
+class SwiGLU(FeedForward):
+    @classmethod
+    def declare(cls, spec, prefix: str) -> List[TensorDecl]:
+        return [TensorDecl(prefix + "gate_proj.weight", (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + "up_proj.weight", (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + "down_proj.weight", (spec.hidden, spec.intermediate))]
+
+    def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        self.spec = spec
+        self.rt = runtime
+        gate, up = tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]
+        if gate.dtype != up.dtype:
+            raise ValueError(f"{prefix}: gate_proj is {gate.dtype} and up_proj is {up.dtype}; they must agree")
+        self.gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.down = tensors[prefix + "down_proj.weight"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.numel() * self.gate_up.element_size() + self.down.numel() * self.down.element_size()
+
+    def forward(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
+        ops = self.rt.ops
+        rows = x.shape[0]
+        gu = torch.empty((rows, 2 * self.spec.intermediate), dtype=x.dtype, device=x.device)
+        ops.gemm(x, self.gate_up, gu)
+        act = torch.empty((rows, self.spec.intermediate), dtype=x.dtype, device=x.device)
+        ops.swiglu(gu, act)
+        ops.gemm(act, self.down, out)
