@@ -1,0 +1,193 @@
+"""The entry point, in the manner of gophonic's root package (gophonic.go:28-237):
+
+    model = Open(path, Options(Format="bf16"))
+    gen = Lane(model, "tokens.Generator")
+    replies = gen.Generate([[1, 2, 3]], ChatOptions(MaxTokens=16))
+    model.Close()
+
+``Open`` loads the model at ``path`` with the first registered format that matches it; formats
+registered later are tried first, so a registered format can take over paths a built-in one
+matches (gophonic.go:176-186).  What a model can do is the set of lanes it provides; ``Lane``
+opens one and ``Supports`` reports whether it can (gophonic.go:89-124).  The built-in format
+matches a folder whose config.json names a registered architecture (qwen3/model.go:110-129 reads
+``model_type`` the same way) and provides the lane "tokens.Generator": generation over token
+ids.  Text lanes need a tokenizer, which this library does not have.
+"""
+from __future__ import annotations
+
+import json
+import os
+import threading
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+from . import registry
+from .sampling.options import Options as ChatOptions
+
+FormatBF16 = "bf16"   # bfloat16 weights and activations on the tensor cores, fp32 residual and statistics
+FormatF32 = "f32"     # everything in true 32-bit, no reduced-precision matrix mode
+
+TokensGenerator = "tokens.Generator"
+
+
+class ErrUnknownFormat(ValueError):
+    pass
+
+
+class ErrUnsupported(ValueError):
+    pass
+
+
+@dataclass
+class Options:
+    """Configures Open.  The zero value picks each model's defaults (gophonic.go:28-39)."""
+    # Threads is accepted for compatibility with gophonic.Options and must not be negative; the
+    # engine runs on the GPU and uses no CPU workers.
+    Threads: int = 0
+    # Format names the weight format: FormatBF16 (default) or FormatF32.
+    Format: str = ""
+    # Device is the CUDA device the model lives on.
+    Device: str = "cuda:0"
+    # CacheTokens sizes the key/value cache (tokens held by live sequences at once, each rounded
+    # up to 64); Batch bounds how many sequences start together.
+    CacheTokens: int = 0
+    Batch: int = 8
+
+
+@dataclass
+class Format:
+    """One kind of model that Open recognizes (gophonic.go:155-172)."""
+    Name: str
+    Match: Callable[[str], bool]
+    Open: Callable[[str, Options], "OpenedModel"]
+    Provides: Sequence[str] = ()
+
+
+class OpenedModel:
+    """A loaded model; its weights are shared by every lane opened from it (gophonic.go:66-84)."""
+
+    def __init__(self, name: str, path: str, close: Optional[Callable[[], None]] = None):
+        self._name, self._path = name, path
+        self._lanes: Dict[str, Callable[[], object]] = {}
+        self._close = close
+
+    def Name(self) -> str:
+        return self._name
+
+    def Path(self) -> str:
+        return self._path
+
+    def Provides(self) -> List[str]:
+        return list(self._lanes)
+
+    def Close(self) -> None:
+        c, self._close, self._lanes = self._close, None, {}
+        if c is not None:
+            c()
+
+
+def Provide(m: OpenedModel, lane: str, open_fn: Callable[[], object]) -> OpenedModel:
+    m._lanes[lane] = open_fn
+    return m
+
+
+def Lane(m: OpenedModel, lane: str):
+    if lane not in m._lanes:
+        raise ErrUnsupported(f"gophonic_b200: {m.Name()} does not provide {lane}")
+    return m._lanes[lane]()
+
+
+def Supports(m: OpenedModel, lane: str) -> bool:
+    return lane in m._lanes
+
+
+_lock = threading.RLock()
+_formats: List[Format] = []
+
+
+def Register(f: Format) -> None:
+    if f.Match is None or f.Open is None:
+        raise ValueError("gophonic_b200: Register of a format without Match or Open")
+    with _lock:
+        _formats.insert(0, f)
+
+
+def Formats() -> List[Format]:
+    with _lock:
+        return list(_formats)
+
+
+def Detect(path: str) -> Optional[Format]:
+    for f in Formats():
+        if f.Match(path):
+            return f
+    return None
+
+
+def Open(path: str, opts: Optional[Options] = None) -> OpenedModel:
+    opts = opts or Options()
+    if opts.Threads < 0:
+        raise ValueError(f"gophonic_b200: invalid thread count {opts.Threads}")
+    if opts.Format not in ("", FormatBF16, FormatF32):
+        raise ErrUnsupported(f"gophonic_b200: unknown weight format '{opts.Format}'")
+    f = Detect(path)
+    if f is None:
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        raise ErrUnknownFormat(f"gophonic_b200: unrecognized model format: {path}")
+    m = f.Open(path, opts)
+    for lane in f.Provides:
+        if not Supports(m, lane):
+            m.Close()
+            raise ErrUnsupported(f"gophonic_b200: format {f.Name} declares {lane}, but its model does not provide it")
+    return m
+
+
+# ---- the built-in format -------------------------------------------------------------------
+def _is_model_dir(path: str) -> bool:
+    try:
+        with open(os.path.join(path, "config.json")) as fh:
+            registry.architecture_of(json.load(fh))
+        return True
+    except (OSError, ValueError, KeyError):
+        return False
+
+
+class TokenGenerator:
+    """Lane "tokens.Generator": replies to prompts given as token ids."""
+
+    def __init__(self, model, opts: Options):
+        from .engine.generate import Generator
+        from .engine.step import Engine
+        from .sampling.sampler import DeviceSampler
+        self.model = model
+        cfg = model.config
+        context = int(getattr(cfg, "max_position_embeddings", model.spec.max_positions))
+        tokens = opts.CacheTokens or min(context, 4096) * opts.Batch
+        self.engine = Engine(model, max_tokens=tokens, max_seq_tokens=min(context, tokens))
+        self.sampler = DeviceSampler(model.spec.vocab, opts.Batch, model.rt.device)
+        self.context = min(context, self.engine.capacity)
+        self.batch = opts.Batch
+
+    def Generate(self, prompts: Sequence[Sequence[int]], options=None, stop_ids: Sequence[int] = (),
+                 on_token=None) -> List[List[int]]:
+        from .engine.generate import Generator
+        g = Generator(self.engine, self.sampler, self.batch, self.context, stop_ids)
+        out = g.generate(prompts, options, on_token)
+        self.stats = g.stats
+        return out
+
+    def Close(self) -> None:
+        self.engine = None
+
+
+def _open_dir(path: str, opts: Options) -> OpenedModel:
+    from .engine.model import Model
+    mode = "float32" if opts.Format == FormatF32 else "bfloat16"
+    model = Model.from_dir(path, dtype=mode, device=opts.Device)
+    m = OpenedModel(model.spec.architecture, path)
+    m.model = model
+    return Provide(m, TokensGenerator, lambda: TokenGenerator(model, opts))
+
+
+Register(Format(Name="model-folder", Match=_is_model_dir, Open=_open_dir, Provides=(TokensGenerator,)))

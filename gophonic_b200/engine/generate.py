@@ -1,0 +1,163 @@
+"""The generation loop above the step function.
+
+Requests are served in batches.  A batch starts together: every prompt of the batch goes
+through one step; after that each live sequence goes on by one token a step.  A sequence ends
+when it draws a stop token (which is not part of its reply: qwen3/chat.go:340-341) or has
+produced its MaxTokens (qwen3/chat.go:305-312, 343); it leaves the batch at once and its slot
+and pages go back to the cache, while the others go on (qwen3asr/batch.go:178-249 keeps the same
+alive/finished bookkeeping for its lanes).  No request joins a running batch; when the batch is
+empty the next one starts, reusing the slots, until no request is left.
+
+The loop decides; it computes nothing.  It talks to an *engine* (``new_sequence``, ``step``,
+``end_sequence``, ``room``) and a *sampler* (``start``, ``select``), so its decisions are tested
+without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Iterable, List, Optional, Sequence, Tuple
+
+from ..sampling.options import Options
+
+
+@dataclass
+class Request:
+    index: int
+    prompt: List[int]
+    options: Options
+    budget: int                      # most tokens this reply may have
+    seed: int
+    reply: List[int] = field(default_factory=list)
+    slot: Optional[int] = None
+    row: Optional[int] = None        # lane of the running batch (the sampler's row)
+    finished: Optional[str] = None   # "stop" | "length"
+
+
+@dataclass
+class GenerationStats:
+    batches: int = 0
+    prefill_tokens: int = 0
+    decode_steps: int = 0
+    decoded_tokens: int = 0
+
+
+class GenerationError(ValueError):
+    pass
+
+
+class Generator:
+    def __init__(self, engine, sampler, max_batch: int, context: int, stop_ids: Iterable[int] = (),
+                 page: int = 64):
+        """``context``: most tokens one sequence may hold (prompt + reply)."""
+        if max_batch <= 0:
+            raise GenerationError(f"max_batch {max_batch}")
+        self.engine = engine
+        self.sampler = sampler
+        self.max_batch = max_batch
+        self.context = context
+        self.stop_ids = frozenset(int(s) for s in stop_ids)
+        self.page = page
+        self.stats = GenerationStats()
+
+    # ---- planning ------------------------------------------------------------------------
+    def _budget(self, prompt_len: int, options: Options) -> int:
+        """Room for the reply: the context left, bounded by MaxTokens (qwen3/chat.go:305-312)."""
+        room = self.context - prompt_len
+        if options.MaxTokens > 0:
+            room = min(room, options.MaxTokens)
+        return room
+
+    def _pages(self, r: Request) -> int:
+        # the last drawn token is never fed back, so a sequence holds at most prompt + budget - 1
+        held = len(r.prompt) + max(r.budget - 1, 0)
+        return (held + self.page - 1) // self.page
+
+    def plan_batch(self, pending: Sequence[Request], free_pages: int) -> int:
+        """How many of the pending requests, in order, start together: at most ``max_batch``, and
+        only as many as can grow to their full length in the pages that are free."""
+        n, used = 0, 0
+        for r in pending[:self.max_batch]:
+            need = self._pages(r)
+            if used + need > free_pages:
+                break
+            used += need
+            n += 1
+        if n == 0 and pending:
+            raise GenerationError(f"request {pending[0].index} needs {self._pages(pending[0])} pages of "
+                                  f"{self.page} tokens and the cache has {free_pages} free")
+        return n
+
+    # ---- the loop ------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], options=None,
+                 on_token: Optional[Callable[[int, int], None]] = None) -> List[List[int]]:
+        """Replies (token ids) for ``prompts``, in order.  ``options``: one ``Options`` for all, or
+        one per prompt.  Request i draws with seed ``Options.Seed + i``.  ``on_token(i, token)`` is
+        called for every token of request i as it is drawn."""
+        if options is None:
+            options = Options()
+        opts = list(options) if isinstance(options, (list, tuple)) else [options] * len(prompts)
+        if len(opts) != len(prompts):
+            raise GenerationError(f"{len(opts)} option sets for {len(prompts)} prompts")
+        pending: List[Request] = []
+        for i, (p, o) in enumerate(zip(prompts, opts)):
+            o.validate()
+            p = [int(t) for t in p]
+            if not p:
+                raise GenerationError(f"request {i}: empty prompt")
+            budget = self._budget(len(p), o)
+            if budget <= 0:
+                raise GenerationError(f"request {i}: a prompt of {len(p)} tokens fills the context of {self.context}")
+            pending.append(Request(i, p, o, budget, (o.Seed + i) & 0xFFFFFFFFFFFFFFFF))
+        results: List[List[int]] = [[] for _ in prompts]
+        while pending:
+            n = self.plan_batch(pending, self.engine.room())
+            batch, pending = pending[:n], pending[n:]
+            self._run_batch(batch, on_token)
+            for r in batch:
+                results[r.index] = r.reply
+        return results
+
+    def _run_batch(self, batch: List[Request], on_token) -> None:
+        self.stats.batches += 1
+        live: List[Request] = []
+        try:
+            for row, r in enumerate(batch):
+                r.slot = self.engine.new_sequence()
+                r.row = row
+                self.sampler.start(row, r.options, r.seed)
+                live.append(r)
+            # all prompts in one step
+            logits = self.engine.step([(r.slot, r.prompt) for r in live])
+            self.stats.prefill_tokens += sum(len(r.prompt) for r in live)
+            while True:
+                tokens = self.sampler.select(logits, [r.row for r in live])
+                still: List[Request] = []
+                for r, t in zip(live, tokens):
+                    self._take(r, int(t), on_token)
+                    if r.finished is None:
+                        still.append(r)
+                    else:
+                        self.engine.end_sequence(r.slot)
+                        r.slot = None
+                live = still
+                if not live:
+                    break
+                # one token each
+                logits = self.engine.step([(r.slot, [r.reply[-1]]) for r in live])
+                self.stats.decode_steps += 1
+                self.stats.decoded_tokens += len(live)
+        finally:
+            for r in batch:
+                if r.slot is not None:
+                    self.engine.end_sequence(r.slot)
+                    r.slot = None
+
+    def _take(self, r: Request, token: int, on_token) -> None:
+        if token in self.stop_ids:
+            r.finished = "stop"
+            return
+        r.reply.append(token)
+        if on_token is not None:
+            on_token(r.index, token)
+        if len(r.reply) >= r.budget:
+            r.finished = "length"

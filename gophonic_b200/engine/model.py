@@ -75,7 +75,7 @@ class Model:
 
     @classmethod
     def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0",
-                    scales: InitScales = InitScales(), layers: Optional[int] = None) -> "Model":
+                    scales: InitScales = InitScales()) -> "Model":
         """Random weights made on the device (for sizes too large to pass through a file)."""
         mode = dtype_mode(dtype)
         spec = config.model_spec()
@@ -95,6 +95,8 @@ class Model:
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None,
                   max_seq_tokens: Optional[int] = None) -> Cache:
+        limit = int(self.spec.max_positions)
+        max_seq_tokens = limit if max_seq_tokens is None else min(limit, int(max_seq_tokens))
         cache = Cache(self.cache_requests(), max_tokens, self.rt.device, self.rt.act_dtype, max_slots, max_seq_tokens)
         capacity = cache.max_pages_per_seq * 64
         for b in self.blocks:

@@ -111,7 +111,7 @@ class Engine:
         self.model = model
         self.device = model.rt.device
         self.cache: Cache = model.new_cache(max_tokens, max_slots, max_seq_tokens)
-        self.capacity = self.cache.max_pages_per_seq * 64
+        self.capacity = min(self.cache.max_pages_per_seq * 64, int(model.spec.max_positions))
         self.max_rows_per_pass = max_rows_per_pass
         self.vocab = model.spec.vocab
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -126,6 +126,10 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def room(self) -> int:
+        """Free pages of 64 tokens."""
+        return self.cache.pages.available()
 
     # ---- the step ------------------------------------------------------------------------
     def validate(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]]):

@@ -1,0 +1,415 @@
+"""Each kernel alone against a plain fp32 (or float64) restatement of the same op, at sizes other
+than the engine's: widths and vocabularies that are no power of two, head sizes in steps of 16,
+odd group counts, rows that straddle tiles, pages in scrambled order.  Where random inputs would
+hide a fault (one far key among hundreds, a window's edge) the inputs are made so that it shows.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from gophonic_b200 import ops
+    return ops
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(device=DEV, dtype=dtype)
+
+
+def close(got: torch.Tensor, ref: torch.Tensor, tol: float):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert err < tol, f"relative error {err:.3e} >= {tol}"
+
+
+def tol_of(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.2e-2
+
+
+# ---- embedding, norm, activation ----------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(ops, dtype):
+    table = rnd(333, 72, dtype=dtype)
+    ids = torch.tensor([0, 332, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty((5, 72), dtype=torch.float32, device=DEV)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [16, 80, 1000, 4100])
+def test_add_rmsnorm(ops, dtype, n):
+    rows, eps = 7, 3e-5
+    h, delta, w = rnd(rows, n, seed=1), rnd(rows, n, seed=2), 1 + 0.1 * rnd(n, seed=3)
+    ref_h = h.double() + delta.double()
+    ref = ref_h / torch.sqrt((ref_h * ref_h).mean(-1, keepdim=True) + eps) * w.double()
+    h1, out = h.clone(), torch.empty((rows, n), dtype=dtype, device=DEV)
+    ops.add_rmsnorm(h1, delta, w, eps, out)
+    close(h1, ref_h, 1e-6)
+    close(out, ref, tol_of(dtype))
+    # without an addend the residual is left alone
+    h2, out2 = h.clone(), torch.empty((rows, n), dtype=dtype, device=DEV)
+    ops.add_rmsnorm(h2, None, w, eps, out2)
+    assert torch.equal(h2, h)
+    close(out2, h.double() / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps) * w.double(), tol_of(dtype))
+    # gathered rows: normalise h[idx] + delta[idx], residual untouched
+    idx = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    h3, out3 = h.clone(), torch.empty((3, n), dtype=dtype, device=DEV)
+    ops.add_rmsnorm(h3, delta, w, eps, out3, idx)
+    assert torch.equal(h3, h)
+    close(out3, ref[idx.long()], tol_of(dtype))
+    # a row's result does not depend on the other rows
+    out4 = torch.empty((1, n), dtype=dtype, device=DEV)
+    ops.add_rmsnorm(h[2:3].clone(), delta[2:3].clone(), w, eps, out4)
+    assert torch.equal(out4[0], out[2])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [8, 136, 1000])
+def test_swiglu(ops, dtype, inter):
+    gu = rnd(5, 2 * inter, dtype=dtype, scale=3.0)
+    out = torch.empty((5, inter), dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    close(out, g / (1 + torch.exp(-g)) * u, 1e-6 if dtype == torch.float32 else 5e-3)
+    big = torch.tensor([[-100.0, 100.0, 0.0, -20.0, 1.0, 1.0, 1.0, 1.0]], device=DEV)
+    o = torch.empty((1, 4), device=DEV)
+    ops.swiglu(big, o)
+    assert torch.isfinite(o).all() and o[0, 1] == 100.0 and o[0, 0] == 0.0
+
+
+# ---- matrix products ----------------------------------------------------------------------
+SHAPES = [(1, 64, 64), (3, 1000, 96), (17, 136, 80), (64, 333, 160), (65, 192, 96), (130, 520, 264), (257, 96, 4104)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("combo", ["fff", "bbf", "bbb", "bfb", "fbf"])
+def test_gemm_simt(ops, M, N, K, combo):
+    dt = {"f": torch.float32, "b": torch.bfloat16}
+    a, w = rnd(M, K, dtype=dt[combo[0]], seed=1), rnd(N, K, dtype=dt[combo[1]], scale=0.1, seed=2)
+    out = torch.empty((M, N), dtype=dt[combo[2]], device=DEV)
+    ops.gemm_simt(a, w, out)
+    close(out, a.double() @ w.double().T, 2e-5 if combo[2] == "f" else 6e-3)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
+    a, w = rnd(70, 200, seed=4), rnd(150, 200, seed=5)
+    full = torch.empty((70, 150), device=DEV)
+    ops.gemm_simt(a, w, full)
+    one = torch.empty((1, 150), device=DEV)
+    ops.gemm_simt(a[67:68].contiguous(), w, one)
+    assert torch.equal(one[0], full[67])
+
+
+@pytest.mark.parametrize("algo", ["skinny", "mma", "tc5"])
+@pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (300, 1000, 512), (2048, 512, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
+    if not hasattr(ops._lib, f"gb_gemm_{algo}"):
+        pytest.skip(f"kernel {algo} is not built")
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    if algo == "skinny" and M > 64:
+        with pytest.raises(ops.KernelError):
+            ops.gemm(a, w, out, algo=algo)
+        return
+    if algo == "tc5" and not ops.tc5_accepts(a, w, out):
+        with pytest.raises(ops.KernelError):
+            ops.gemm(a, w, out, algo=algo)
+        return
+    ops.gemm(a, w, out, algo=algo)
+    close(out, a.double() @ w.double().T, 2e-5 if out_dtype == torch.float32 else 6e-3)
+
+
+def test_gemm_dispatch_never_puts_float32_on_tensor_cores(ops):
+    a, w = rnd(4, 64), rnd(8, 64)
+    out = torch.empty((4, 8), device=DEV)
+    assert ops.gemm(a, w, out) == "simt"
+    a16 = a.to(torch.bfloat16)
+    assert ops.gemm(a16, w, out) == "simt"  # a weight stored in 32-bit stays on the fp32 kernel
+    with pytest.raises(ops.KernelError):
+        ops.gemm_simt(a.cpu(), w, out)
+
+
+# ---- fused per-head norm + rotation + cache write ------------------------------------------
+def paged(n_pages, kvh, d, dtype, seed):
+    k = rnd(n_pages, kvh, 64, d, dtype=dtype, seed=seed)
+    v = rnd(n_pages, kvh, 64, d, dtype=dtype, seed=seed + 1)
+    return k, v
+
+
+def gather_kv(plane, table_row, length):
+    """[length, kvh, d] of one sequence out of the paged plane."""
+    pages = plane[table_row[: (length + 63) // 64].long()]          # [p, kvh, 64, d]
+    return pages.permute(0, 2, 1, 3).reshape(-1, plane.shape[1], plane.shape[3])[:length]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kvh,d,rot,qk_norm", [(4, 2, 16, 16, True), (5, 1, 48, 48, True), (6, 3, 32, 16, True),
+                                                    (2, 2, 128, 128, False), (3, 1, 80, 0, True)])
+def test_qk_norm_rope_kv_write(ops, dtype, heads, kvh, d, rot, qk_norm):
+    eps, theta = 2e-6, 5000.0
+    lens = [3, 70, 1]           # rows per sequence in this step
+    past = [0, 60, 130]         # tokens already cached
+    slots = [2, 0, 5]
+    rows = sum(lens)
+    n_pages, max_pages = 16, 4
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    table = torch.zeros((6, max_pages), dtype=torch.int32)
+    for i, s in enumerate(slots):
+        table[s] = perm[i * 4:(i + 1) * 4]
+    table = table.to(DEV)
+    k_plane, v_plane = paged(n_pages, kvh, d, dtype, 3)
+    k0, v0 = k_plane.clone(), v_plane.clone()
+    qkv = rnd(rows, (heads + 2 * kvh) * d, dtype=dtype, seed=9)
+    qkv0 = qkv.clone()
+    qw, kw = (1 + 0.1 * rnd(d, seed=5), 1 + 0.1 * rnd(d, seed=6)) if qk_norm else (None, None)
+    row_pos = torch.tensor(sum(([p + j for j in range(n)] for n, p in zip(lens, past)), []), dtype=torch.int32, device=DEV)
+    row_seq = torch.tensor(sum(([i] * n for i, n in enumerate(lens)), []), dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    cos = sin = None
+    if rot:
+        c, s = P.rope_tables(np.arange(256), rot, theta)
+        cos, sin = (torch.tensor(x, dtype=torch.float32, device=DEV) for x in (c, s))
+    ops.qk_norm_rope_kv_write(qkv, heads, kvh, d, qw, kw, eps, cos, sin, rot, row_pos, row_seq, seq_slot,
+                              table, 0, k_plane, v_plane, True)
+    # reference in float64 from the inputs
+    x = qkv0.double().cpu().numpy()
+    q = x[:, :heads * d].reshape(rows, heads, d)
+    k = x[:, heads * d:(heads + kvh) * d].reshape(rows, kvh, d)
+    v = x[:, (heads + kvh) * d:].reshape(rows, kvh, d)
+    if qk_norm:
+        q, k = P.rms_norm(q, qw.double().cpu().numpy(), eps), P.rms_norm(k, kw.double().cpu().numpy(), eps)
+    if rot:
+        c, s = P.rope_tables(row_pos.cpu().numpy(), rot, theta)
+        q, k = P.apply_rope(q, c, s), P.apply_rope(k, c, s)
+    tol = tol_of(dtype)
+    close(qkv[:, :heads * d], torch.tensor(q.reshape(rows, -1)), tol)
+    assert torch.equal(qkv[:, heads * d:], qkv0[:, heads * d:])  # k and v columns of the buffer are not changed
+    r = 0
+    touched = torch.zeros(n_pages, 64, dtype=torch.bool)
+    for i, (n, p0, slot) in enumerate(zip(lens, past, slots)):
+        kk = gather_kv(k_plane, table[slot], p0 + n)[p0:]
+        vv = gather_kv(v_plane, table[slot], p0 + n)[p0:]
+        close(kk, torch.tensor(k[r:r + n]), tol)
+        assert torch.equal(vv, qkv0[r:r + n, (heads + kvh) * d:].reshape(n, kvh, d))
+        for pos in range(p0, p0 + n):
+            touched[table[slot, pos // 64].item(), pos % 64] = True
+        r += n
+    # nothing else in the planes moved
+    keep = ~touched.to(DEV)
+    assert torch.equal(k_plane.permute(0, 2, 1, 3)[keep], k0.permute(0, 2, 1, 3)[keep])
+    assert torch.equal(v_plane.permute(0, 2, 1, 3)[keep], v0.permute(0, 2, 1, 3)[keep])
+    # a run that reads another run's cache writes nothing
+    qkv2, k2, v2 = qkv0.clone(), k0.clone(), v0.clone()
+    ops.qk_norm_rope_kv_write(qkv2, heads, kvh, d, qw, kw, eps, cos, sin, rot, row_pos, row_seq, seq_slot,
+                              table, 0, k2, v2, False)
+    assert torch.equal(k2, k0) and torch.equal(v2, v0) and torch.equal(qkv2[:, :heads * d], qkv[:, :heads * d])
+
+
+# ---- attention ------------------------------------------------------------------------------
+def attention_reference(q, k_plane, v_plane, table, slots, q_lens, kv_lens, heads, kvh, d, scale, window):
+    """float64, one sequence at a time, from the paged planes."""
+    out = []
+    r = 0
+    for slot, ql, kl in zip(slots, q_lens, kv_lens):
+        k = gather_kv(k_plane, table[slot], kl).double().cpu().numpy()
+        v = gather_kv(v_plane, table[slot], kl).double().cpu().numpy()
+        qq = q[r:r + ql].double().cpu().numpy().reshape(ql, heads, d)
+        # rows are the last ql positions of kl keys: pad queries in front and take the tail
+        full_q = np.zeros((kl, heads, d))
+        full_q[kl - ql:] = qq
+        out.append(P.causal_attention(full_q, k, v, scale, window)[kl - ql:].reshape(ql, heads * d))
+        r += ql
+    return torch.tensor(np.concatenate(out, 0))
+
+
+def attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, window=0, splits=1, algo="auto", seed=0, craft=None):
+    nseq = len(q_lens)
+    max_pages = (max(kv_lens) + 63) // 64
+    n_pages = nseq * max_pages + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).to(torch.int32)
+    slots = list(range(nseq - 1, -1, -1))
+    table = torch.zeros((nseq, max_pages), dtype=torch.int32)
+    for i, s in enumerate(slots):
+        table[s] = perm[i * max_pages:(i + 1) * max_pages]
+    table = table.to(DEV)
+    k_plane, v_plane = paged(n_pages, kvh, d, dtype, seed + 1)
+    rows = sum(q_lens)
+    stride = heads * d + 24
+    qbuf = rnd(rows, stride, dtype=dtype, seed=seed + 2)
+    q = qbuf[:, :heads * d]
+    if craft is not None:
+        craft(q, k_plane, v_plane, table, slots)
+    out = torch.full((rows, heads * d), float("nan"), dtype=dtype, device=DEV)
+    starts = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+    mk = lambda x: torch.tensor(list(x), dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, d, splits), dtype=torch.float32, device=DEV)
+    used = ops.attention(q, out, k_plane, v_plane, table, 0, mk(slots), mk(starts), mk(q_lens), mk(kv_lens), nseq,
+                         max(q_lens), heads, kvh, d, scale, window, splits, scratch, algo=algo)
+    ref = attention_reference(q, k_plane, v_plane, table, slots, q_lens, kv_lens, heads, kvh, d, scale, window)
+    return out, ref, used
+
+
+GEOMS = [(4, 2, 16), (6, 3, 32), (5, 1, 48), (8, 8, 64), (7, 1, 80), (4, 1, 96), (2, 1, 112), (32, 8, 128), (20, 1, 32),
+         (2, 2, 256)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kvh,d", GEOMS)
+def test_attention_prompts(ops, dtype, heads, kvh, d):
+    """Whole prompts, prompts that continue a cached prefix, and a single row, in one batch."""
+    out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens=[70, 5, 1, 33], kv_lens=[70, 69, 130, 33])
+    close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kvh,d", GEOMS)
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_attention_single_tokens(ops, dtype, heads, kvh, d, splits):
+    out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens=[1, 1, 1, 1, 1], kv_lens=[1, 64, 65, 700, 333],
+                                 splits=splits)
+    close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("algo", ["simt", "auto"])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, algo):
+    """One query and one key 500 positions back are scaled so that key takes all the weight: the
+    output must be that key's value, for a prompt row and for a single-token row."""
+    heads, kvh, d = 4, 2, 64
+    far = 37
+
+    def craft(q, k_plane, v_plane, table, slots):
+        for seq, slot in enumerate(slots):
+            page, off = table[slot, far // 64].item(), far % 64
+            k_plane[page, :, off] = 0
+            k_plane[page, :, off, 3] = 30.0
+        q[:] = q * 0.05
+        q[:, 3::d] = 30.0
+    for q_lens, kv_lens, splits in (([520], [520], 1), ([1, 1], [538, 100], 1), ([1, 1], [538, 100], 4)):
+        out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, splits=splits, algo=algo, craft=craft)
+        close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+        # the last row of the first sequence sits > 480 keys after the far key and still returns its value
+        assert ref[q_lens[0] - 1].abs().max() > 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_window_edge(ops, dtype):
+    """With a window of w the key at distance w - 1 is the last one seen: a dominant key placed
+    exactly there is found, one step further it is not."""
+    heads, kvh, d, w = 2, 1, 32, 70
+    for dist, q_lens, kv_lens in ((w - 1, [1], [200]), (w, [1], [200]), (w - 1, [90], [200]), (w, [90], [200])):
+        target = kv_lens[0] - 1 - dist
+
+        def craft(q, k_plane, v_plane, table, slots):
+            page, off = table[slots[0], target // 64].item(), target % 64
+            k_plane[page, :, off] = 0
+            k_plane[page, :, off, 5] = 40.0
+            q[:] = q * 0.05
+            q[:, 5::d] = 40.0
+        out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, window=w, craft=craft)
+        close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+
+
+def test_attention_refuses_what_it_cannot_take(ops):
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        attention_case(ops, torch.float32, 2, 1, 272, [3], [3])
+    with pytest.raises(ops.KernelError, match="single-token"):
+        attention_case(ops, torch.float32, 2, 1, 32, [3], [3], splits=2)
+
+
+# ---- selection --------------------------------------------------------------------------------
+def test_argmax_first_maximum_nan_and_ties(ops):
+    V = 151936
+    x = rnd(6, V)
+    x[0, 777] = x[0, 123456] = 50.0           # tie: the lower index
+    x[1, 5] = float("nan")
+    x[1, 9000] = 60.0
+    x[2] = float("nan")                        # all NaN: index 0
+    x[3, V - 1] = 70.0
+    x[4] = -float("inf")
+    x[5, 0] = 80.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.argmax(x, out)
+    assert out.tolist() == [777, 9000, 0, V - 1, 0, 0]
+    ref = [P.argmax_first(r) for r in x.cpu().numpy()]
+    assert out.tolist() == ref
+
+
+@pytest.mark.parametrize("V", [23, 1000, 151936])
+def test_sampler_matches_the_plain_sampler(ops, V):
+    rows = 12
+    logits = rnd(rows, V, scale=2.0, seed=V)
+    logits[3, : min(V, 40)] = 1.5           # many ties at the threshold
+    temps = [0.8, 1.0, 0.0, 0.7, 1.3, 0.5, 1.0, 1.0, 2.0, 0.9, 1.0, 0.3]
+    ks = [20, 0, 5, 10, 1, 2000, 50, 3, 0, 7, 1024, 2]
+    ps = [0.0, 0.9, 0.5, 0.0, 0.0, 0.95, 1.0, 0.5, 0.2, 0.0, 0.99, 0.0]
+    for draw0 in (0, 17):
+        seeds = [1000 + i for i in range(rows)]
+        draws = [draw0 + i for i in range(rows)]
+        mk = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        ops.sample(logits, mk(temps, torch.float32), mk(ks, torch.int32), mk(ps, torch.float32),
+                   mk(seeds, torch.int64), mk(draws, torch.int64), out)
+        host = logits.cpu().numpy()
+        for r in range(rows):
+            tok, cand, probs = P.sample_token(host[r], temps[r], ks[r], ps[r], seeds[r], draws[r])
+            got = out[r].item()
+            if got != tok:
+                # expf on the device and exp on the host may differ in the last place: the draw may
+                # then fall on the other side of a boundary between neighbouring candidates
+                assert cand is not None and got in cand
+                i, j = cand.index(got), cand.index(tok)
+                assert abs(i - j) == 1, (r, got, tok)
+
+
+def test_sampler_distribution_and_batch_independence(ops):
+    V = 300
+    base = torch.full((V,), -30.0)
+    base[[7, 100, 250]] = torch.tensor([math.log(5.0), math.log(3.0), math.log(2.0)])
+    n = 4000
+    logits = base.repeat(n, 1).to(DEV)
+    mk = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, mk([1.0] * n, torch.float32), mk([3] * n, torch.int32), mk([0.0] * n, torch.float32),
+               mk([42] * n, torch.int64), mk(list(range(n)), torch.int64), out)
+    counts = torch.bincount(out.long().cpu(), minlength=V).double() / n
+    assert set(torch.nonzero(counts).flatten().tolist()) <= {7, 100, 250}      # never outside top-k
+    assert abs(counts[7] - 0.5) < 0.035 and abs(counts[100] - 0.3) < 0.035 and abs(counts[250] - 0.2) < 0.035
+    # equal (seed, draw) -> equal token, whatever else is in the batch
+    one = torch.empty(1, dtype=torch.int32, device=DEV)
+    for i in (0, 1234, 3999):
+        ops.sample(logits[:1], mk([1.0], torch.float32), mk([3], torch.int32), mk([0.0], torch.float32),
+                   mk([42], torch.int64), mk([i], torch.int64), one)
+        assert one.item() == out[i].item()
+
+
+def test_presence_penalty_and_seen_bitmap(ops):
+    V, rows = 70, 3
+    logits = torch.zeros((rows, V), device=DEV)
+    seen = torch.zeros((4, 3), dtype=torch.int32, device=DEV)
+    seen_row = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
+    toks = torch.tensor([5, 69, 33], dtype=torch.int32, device=DEV)
+    ops.mark_seen(toks, V, seen, seen_row)
+    ops.mark_seen(torch.tensor([64, 69, 33], dtype=torch.int32, device=DEV), V, seen, seen_row)
+    pres = torch.tensor([1.5, 0.0, 2.0], device=DEV)
+    ops.presence_penalty(logits, seen, seen_row, pres)
+    want = torch.zeros((rows, V))
+    want[0, 5] = want[0, 64] = -1.5
+    want[2, 33] = -2.0      # marked twice, penalised once; row 1 has no penalty
+    assert torch.equal(logits.cpu(), want)

@@ -1,0 +1,282 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every way of
+cutting the work: each request alone and whole; with the last 32 tokens one by one; in batches
+of unequal lengths whose shorter requests end earlier, one batch after another so that slots and
+pages are used again; long decoding; the first tokens of a sequence; and through bin/trace_run.
+
+Tolerances (relative to the largest reference logit of the compared block, fixed here once):
+32-bit 1e-4, bfloat16 3e-2.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
+    return float(np.max(np.abs(got.astype(np.float64) - ref)) / np.max(np.abs(ref)))
+
+
+def requests_for(cfg, seed, lengths):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, cfg["vocab_size"], size=n).tolist() for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def engines(model_dirs):
+    from gophonic_b200.engine import Engine, Model
+    cache = {}
+
+    def get(name, dtype, max_tokens=4096):
+        key = (name, dtype, max_tokens)
+        if key not in cache:
+            cache[key] = Engine(Model.from_dir(model_dirs[name], dtype=dtype), max_tokens=max_tokens)
+        return cache[key]
+    return get
+
+
+@pytest.fixture(scope="module")
+def references(plain_models):
+    memo = {}
+
+    def get(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in memo:
+            cfg, w = plain_models[name]
+            memo[key] = P.forward_logits(list(tokens), cfg, w)
+        return memo[key]
+    return get
+
+
+LENGTHS = {"A": [1, 5, 17, 70, 131], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 129]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "A32"])
+def test_each_request_alone_and_whole(engines, references, plain_models, name, dtype):
+    eng = engines(name, dtype)
+    cfg, _ = plain_models[name]
+    for rid, toks in requests_for(cfg, 1, LENGTHS[name[0]]).items():
+        slot = eng.new_sequence()
+        logits = eng.step([(slot, toks)], [list(range(len(toks)))]).cpu().numpy()
+        eng.end_sequence(slot)
+        ref = references(name, toks)
+        assert logits.shape == ref.shape
+        assert rel_err(logits, ref) < TOL[dtype], (rid, len(toks))
+        if dtype == "float32":
+            assert (logits.argmax(-1) == ref.argmax(-1)).mean() > 0.99
+    eng.cache.check()
+    assert eng.cache.pages.held() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(engines, references, plain_models, name, dtype):
+    eng = engines(name, dtype)
+    cfg, _ = plain_models[name]
+    for rid, toks in requests_for(cfg, 2, [33, 70, 97, 160]).items():
+        ref = references(name, toks)
+        cut = len(toks) - 32
+        slot = eng.new_sequence()
+        got = [eng.step([(slot, toks[:cut])], [list(range(cut))]).cpu().numpy()]
+        for t in toks[cut:]:
+            got.append(eng.step([(slot, [t])], [[0]]).cpu().numpy())
+        eng.end_sequence(slot)
+        got = np.concatenate(got, 0)
+        # find the first position that is off, to say what is special about its place
+        err = np.max(np.abs(got - ref), axis=-1) / np.max(np.abs(ref))
+        bad = np.nonzero(err >= TOL[dtype])[0]
+        assert bad.size == 0, f"{rid}: first wrong position {bad[0]} of {len(toks)} (decoding starts at {cut})"
+    assert eng.cache.pages.held() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_batches_of_unequal_lengths_one_after_another(engines, references, plain_models, name, dtype):
+    """Each batch starts together with unequal prompts, then one token each; shorter requests end
+    earlier; the next batch reuses the slots and pages the last one gave back."""
+    eng = engines(name, dtype, 1024)
+    cfg, _ = plain_models[name]
+    rng = np.random.default_rng(5)
+    plans = [  # (prompt length, decoded tokens) per request of a batch
+        [(5, 8), (11, 3), (17, 12), (1, 20)],
+        [(1, 12), (7, 1), (23, 30), (40, 5), (64, 2), (63, 3)],
+        [(130, 4), (2, 70)],
+        [(9, 9), (70, 70), (33, 1)],
+    ]
+    seen_slots = []
+    for b, plan in enumerate(plans):
+        toks = [rng.integers(0, cfg["vocab_size"], size=p + d).tolist() for p, d in plan]
+        refs = [references(name, t) for t in toks]
+        slots = [eng.new_sequence() for _ in plan]
+        seen_slots.append(set(slots))
+        got = [[] for _ in plan]
+        first = eng.step([(slots[i], toks[i][:p]) for i, (p, _) in enumerate(plan)],
+                         [list(range(p)) for p, _ in plan]).cpu().numpy()
+        o = 0
+        for i, (p, _) in enumerate(plan):
+            got[i].append(first[o:o + p])
+            o += p
+        live = list(range(len(plan)))
+        step = 0
+        while live:
+            live = [i for i in live if step < plan[i][1]]
+            if not live:
+                break
+            out = eng.step([(slots[i], [toks[i][plan[i][0] + step]]) for i in live], [[0]] * len(live)).cpu().numpy()
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+            step += 1
+            for i in list(live):
+                if step >= plan[i][1]:
+                    eng.end_sequence(slots[i])  # ends earlier than the others
+                    slots[i] = None
+        for i in range(len(plan)):
+            if slots[i] is not None:
+                eng.end_sequence(slots[i])
+            g = np.concatenate(got[i], 0)
+            err = np.max(np.abs(g - refs[i]), axis=-1) / np.max(np.abs(refs[i]))
+            bad = np.nonzero(err >= TOL[dtype])[0]
+            assert bad.size == 0, (f"batch {b} request {i} (prompt {plan[i][0]}, decoded {plan[i][1]}): "
+                                   f"first wrong position {bad[0]}")
+        eng.cache.check()
+        assert eng.cache.pages.held() == 0 and eng.cache.slots.held() == 0
+    assert seen_slots[0] & seen_slots[1], "slots are used again"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(engines, references, plain_models, dtype):
+    eng = engines("B", dtype)
+    cfg, _ = plain_models["B"]
+    toks = requests_for(cfg, 9, [330])["r0"]
+    ref = references("B", toks)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, [t])], [[0]]).cpu().numpy() for t in toks]
+    eng.end_sequence(slot)
+    got = np.concatenate(got, 0)
+    err = np.max(np.abs(got - ref), axis=-1) / np.max(np.abs(ref))
+    bad = np.nonzero(err >= TOL[dtype])[0]
+    assert bad.size == 0, f"first wrong position {bad[0]}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(engines, references, plain_models, dtype):
+    eng = engines("A", dtype)
+    cfg, _ = plain_models["A"]
+    for tok in (0, 1, cfg["vocab_size"] - 1):
+        slot = eng.new_sequence()
+        a = eng.step([(slot, [tok])]).cpu().numpy()          # default: the last place
+        b = eng.step([(slot, [tok, tok])], [[0, 1]]).cpu().numpy()
+        eng.end_sequence(slot)
+        ref = references("A", [tok, tok, tok])
+        assert rel_err(a, ref[:1]) < TOL[dtype] and rel_err(b, ref[1:]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_fed_in_pieces_and_in_row_chunks(model_dirs, references, plain_models, dtype):
+    """A prompt cut into steps of 7, and a step cut into passes of 16 rows, give the whole
+    prompt's logits."""
+    from gophonic_b200.engine import Engine, Model
+    cfg, _ = plain_models["B"]
+    reqs = requests_for(cfg, 12, [90, 37, 5])
+    model = Model.from_dir(model_dirs["B"], dtype=dtype)
+    eng = Engine(model, max_tokens=1024, max_rows_per_pass=16)
+    slots = {rid: eng.new_sequence() for rid in reqs}
+    out = eng.step([(slots[r], t) for r, t in reqs.items()], [list(range(len(t))) for t in reqs.values()]).cpu().numpy()
+    assert eng.passes == (90 + 37 + 5 + 15) // 16
+    o = 0
+    for rid, t in reqs.items():
+        assert rel_err(out[o:o + len(t)], references("B", t)) < TOL[dtype], rid
+        o += len(t)
+        eng.end_sequence(slots[rid])
+    eng2 = Engine(model, max_tokens=256)
+    t = reqs["r0"]
+    slot = eng2.new_sequence()
+    got = np.concatenate([eng2.step([(slot, t[i:i + 7])], [list(range(len(t[i:i + 7])))]).cpu().numpy()
+                          for i in range(0, len(t), 7)], 0)
+    assert rel_err(got, references("B", t)) < TOL[dtype]
+
+
+def test_where_a_sequence_lies_in_the_cache_changes_nothing(engines, plain_models):
+    eng = engines("A", "float32", 1024)
+    cfg, _ = plain_models["A"]
+    toks = requests_for(cfg, 21, [100])["r0"]
+    s = eng.new_sequence()
+    a = eng.step([(s, toks)], [list(range(100))]).cpu().numpy()
+    eng.end_sequence(s)
+    # occupy and dirty other slots and pages, then run the same request among them
+    others = [eng.new_sequence() for _ in range(3)]
+    eng.step([(o, requests_for(cfg, 30 + i, [70])["r0"]) for i, o in enumerate(others)])
+    eng.end_sequence(others[1])
+    s = eng.new_sequence()
+    b = eng.step([(s, toks), (others[0], [1])], [list(range(100)), []]).cpu().numpy()
+    for x in (s, others[0], others[2]):
+        eng.end_sequence(x)
+    assert np.max(np.abs(a - b)) <= 1e-5 * np.max(np.abs(a))
+
+
+def test_refused_steps_leave_the_cache_as_it_was(engines, plain_models):
+    from gophonic_b200.cache import CacheFull
+    from gophonic_b200.engine import StepError
+    eng = engines("A", "float32", 256)
+    cfg, _ = plain_models["A"]
+    s = eng.new_sequence()
+    eng.step([(s, [1, 2, 3])])
+    held = eng.cache.pages.held()
+    for bad, exc, word in [([(s, [cfg["vocab_size"]])], StepError, "outside"), ([(s, [])], StepError, "no tokens"),
+                           ([(s, [1]), (s, [2])], StepError, "twice"), ([(99, [1])], StepError, "not live"),
+                           ([(s, [1] * 300)], (StepError, CacheFull), "")]:
+        with pytest.raises(exc, match=word):
+            eng.step(bad)
+        assert eng.length(s) == 3 and eng.cache.pages.held() == held
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([(s, [1])], [[1]])
+    eng.end_sequence(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, references, plain_models, tmp_path, dtype):
+    """bin/trace_run, as a user calls it: steps on stdin, <step>.f32 files out, 'done <step>' lines."""
+    cfg, _ = plain_models["B"]
+    reqs = requests_for(cfg, 40, [40, 9, 70])
+    a, b, c = reqs["r0"], reqs["r1"], reqs["r2"]
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": list(range(30))},
+                                {"id": "b", "tokens": b[:8], "want": [0, 7]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": [a[30]], "want": [0]}, {"id": "b", "tokens": [b[8]], "want": [0]}],
+         "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": [a[31]], "want": []}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": [a[32]], "want": [0]}], "end": ["a"]},
+        {"step": 4, "entries": [{"id": "c", "tokens": c, "want": [0, 69]}], "end": ["c"]},
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["B"],
+                           "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    V = cfg["vocab_size"]
+    ra, rb, rc = references("B", a), references("B", b), references("B", c)
+
+    def load(i):
+        return np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+    s0 = load(0)
+    assert s0.shape[0] == 32
+    assert rel_err(s0[:30], ra[:30]) < TOL[dtype] and rel_err(s0[30:], rb[[0, 7]]) < TOL[dtype]
+    s1 = load(1)
+    assert rel_err(s1[:1], ra[30:31]) < TOL[dtype] and rel_err(s1[1:], rb[8:9]) < TOL[dtype]
+    assert not (out / "2.f32").exists()
+    assert rel_err(load(3), ra[32:33]) < TOL[dtype]
+    assert rel_err(load(4), rc[[0, 69]]) < TOL[dtype]
