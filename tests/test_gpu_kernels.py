@@ -86,7 +86,7 @@ def test_swiglu(ops, dtype, inter):
     big = torch.tensor([[-100.0, 100.0, 0.0, -20.0, 1.0, 1.0, 1.0, 1.0]], device=DEV)
     o = torch.empty((1, 4), device=DEV)
     ops.swiglu(big, o)
-    assert torch.isfinite(o).all() and o[0, 1] == 100.0 and o[0, 0] == 0.0
+    assert torch.isfinite(o).all() and o[0, 1] == 100.0 and abs(o[0, 0].item()) < 1e-30
 
 
 # ---- matrix products ----------------------------------------------------------------------
