@@ -1,0 +1,253 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Qwen3-8B-shaped model with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with every sequence's
+context filling to 4096, timed on the device over exactly K decode steps (one token per sequence
+a step, token selection included).  ``e2e`` is the same loop driven as a user drives it, host
+token ids in and host token ids out every step.  ``prefill`` is one prompt of 2,048 tokens,
+``points`` are decode at batch 1 and 64, ``roofline`` divides the bytes a decode step has to
+read (every weight once, the live sequences' keys and values) by its time.
+"""
+import argparse
+import dataclasses
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    """(hbm GB/s, bf16 TFLOP/s burst, which) from MEASURED_PEAKS.json, else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except (OSError, ValueError, KeyError):
+        return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        self.file.close()
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_setup(engine, batch, start_len, torch):
+    """``batch`` live sequences whose caches hold ``start_len`` tokens of synthetic keys and values."""
+    slots = [engine.new_sequence() for _ in range(batch)]
+    grow = [(s, start_len) for s in slots]
+    engine.cache.reserve(grow)
+    engine.cache.commit(grow)
+    return slots
+
+
+def fill_cache_random(engine, torch):
+    g = torch.Generator(device=engine.device)
+    g.manual_seed(1)
+    for planes in list(engine.cache._k.values()) + list(engine.cache._v.values()):
+        for i in range(planes.shape[0]):  # plane by plane keeps the temporary small
+            planes[i].normal_(0.0, 1.0, generator=g)
+
+
+def time_decode(engine, sampler, batch, steps, warmup, torch, ops, e2e):
+    """Returns (ms per step on the device, ms per step wall for the host-in/host-out loop, launches per step, h2d, d2h)."""
+    import numpy as np
+    start_len = CONTEXT - (steps + warmup) - 1
+    slots = decode_setup(engine, batch, start_len, torch)
+    rng = np.random.default_rng(0)
+    tokens = rng.integers(0, engine.vocab, size=batch).tolist()
+    rows = list(range(batch))
+    from gophonic_b200.sampling import Options
+    for r in rows:
+        sampler.start(r, Options(), r)
+    out = {}
+    try:
+        for _ in range(warmup):
+            logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
+            tokens = sampler.select(logits, rows)
+        torch.cuda.synchronize()
+        if not e2e:
+            l0 = ops.launches
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dev_tokens = None
+            ev0.record()
+            for _ in range(steps):
+                logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
+                dev_tokens = sampler.select_device(logits, rows)
+            ev1.record()
+            torch.cuda.synchronize()
+            out["ms"] = ev0.elapsed_time(ev1) / steps
+            out["launches"] = (ops.launches - l0) / steps
+        else:
+            up0 = engine.stager.bytes_uploaded
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
+                tokens = sampler.select(logits, rows)   # device -> host read of the step's result
+            torch.cuda.synchronize()
+            out["ms"] = (time.perf_counter() - t0) * 1e3 / steps
+            out["h2d"] = (engine.stager.bytes_uploaded - up0) // steps
+            out["d2h"] = 4 * batch
+        out["kv_tokens"] = sum(engine.length(s) for s in slots)
+    finally:
+        for s in slots:
+            engine.end_sequence(s)
+    return out
+
+
+def time_prefill(engine, tokens, iters, warmup, torch):
+    import numpy as np
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, engine.vocab, size=tokens).tolist()
+    times = []
+    for i in range(warmup + iters):
+        slot = engine.new_sequence()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        engine.step([(slot, prompt)])
+        ev1.record()
+        torch.cuda.synchronize()
+        engine.end_sequence(slot)
+        if i >= warmup:
+            times.append(ev0.elapsed_time(ev1))
+    return statistics.median(times)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "GetStream/gophonic is a Go module (no setup.py/pyproject; pip "
+                          "refuses it), there is no Go toolchain here, and its GPU paths are Metal/WebGPU only"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": f"this library runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    from gophonic_b200 import ops
+    from gophonic_b200.config import Qwen3Config
+    from gophonic_b200.engine import Engine, Model
+    from gophonic_b200.sampling import DeviceSampler
+
+    full_layers = 36
+    layers = args.layers or full_layers
+    cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8,
+                      head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=40960,
+                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    hbm_peak, tflops_peak, which = peaks()
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    max_batch = args.batch if args.no_points else max(args.batch, 64)
+    engine = Engine(model, max_tokens=max_batch * CONTEXT, max_slots=max_batch, max_seq_tokens=CONTEXT)
+    fill_cache_random(engine, torch)
+    sampler = DeviceSampler(cfg.vocab_size, max_batch, engine.device)
+    weight_bytes = model.weight_bytes_per_step()
+    kv_bytes_per_token = engine.cache.bytes_per_token()
+
+    clocks = ClockSampler()
+    clocks.start()
+    dev = time_decode(engine, sampler, args.batch, args.steps, warmup, torch, ops, e2e=False)
+    clock_info = clocks.stop()
+    e2e = time_decode(engine, sampler, args.batch, args.steps, warmup, torch, ops, e2e=True)
+
+    step_bytes = weight_bytes + kv_bytes_per_token * dev["kv_tokens"]
+    achieved = step_bytes / (dev["ms"] * 1e-3) / 1e9
+    value = args.batch / (dev["ms"] * 1e-3)
+    line = {
+        "metric": "Qwen3-8B decode tok/s @ batch 8, context 4096 (random weights, bf16)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(dev["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, random token ids, cache pre-filled with random keys/values",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B-shaped", "layers": layers, "layers_full": full_layers, "hidden": 4096, "heads": 32,
+                   "kv_heads": 8, "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "parallelism": "single-gpu", "l2": "step reads >15 GB of weights, larger than L2",
+                   "peaks": which},
+        "e2e": {"value": round(args.batch / (e2e["ms"] * 1e-3), 1), "unit": "tok/s",
+                "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])},
+        "gpu_launches": int(round(dev["launches"] * args.steps)),
+        "clocks": clock_info,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                     "frac": round(achieved / hbm_peak, 4)},
+    }
+    if not args.no_points:
+        ms = time_prefill(engine, PREFILL_TOKENS, iters=3, warmup=3, torch=torch)
+        T = PREFILL_TOKENS
+        params = (weight_bytes - model.head.numel() * model.head.element_size()) // 2
+        flops = 2.0 * T * params + 2.0 * cfg.num_attention_heads * cfg.head_dim * T * T * layers + 2.0 * model.head.numel()
+        line["prefill"] = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
+                           "frac": round(flops / (ms * 1e-3) / (tflops_peak * 1e12), 4)}
+        points = {}
+        for b in (1, 64):
+            d = time_decode(engine, sampler, b, min(args.steps, 10), 3, torch, ops, e2e=False)
+            points[f"decode_b{b}"] = round(b / (d["ms"] * 1e-3), 1)
+            bytes_b = weight_bytes + kv_bytes_per_token * d["kv_tokens"]
+            points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (d["ms"] * 1e-3) / 1e9 / hbm_peak, 4)
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -71,13 +71,68 @@ def choose_splits(units: int, max_kv_len: int, sm_count: int = 148) -> int:
     return int(max(1, min(by_len, by_occupancy, 32)))
 
 
+class HostStager:
+    """Pinned host buffers for the per-step upload of row metadata.  A small ring, each buffer
+    guarded by an event recorded after its copy, so the host may run ahead of the device without
+    overwriting a buffer whose copy has not happened yet."""
+
+    def __init__(self, device, ring: int = 4):
+        self.device = torch.device(device)
+        self.ring = ring
+        self.bufs: List[Optional[torch.Tensor]] = [None] * ring
+        self.events: List[Optional[torch.cuda.Event]] = [None] * ring
+        self.at = 0
+        self.bytes_uploaded = 0
+
+    def upload(self, n: int, fill) -> torch.Tensor:
+        """A device int32 tensor of ``n`` elements whose contents ``fill(numpy_view)`` writes."""
+        i = self.at
+        self.at = (self.at + 1) % self.ring
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i] is None or self.bufs[i].numel() < n:
+            self.bufs[i] = torch.empty(max(1024, 2 * n), dtype=torch.int32).pin_memory()
+        host = self.bufs[i][:n]
+        fill(host.numpy())
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        dev.copy_(host, non_blocking=True)
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+        self.bytes_uploaded += 4 * n
+        return dev
+
+
 def build_batch(pieces: Sequence[Tuple[int, Sequence[int], int]], device, sm_count: int = 148,
-                want_rows: Optional[Sequence[int]] = None) -> Tuple[StepBatch, Optional[torch.Tensor]]:
+                want_rows: Optional[Sequence[int]] = None,
+                stager: Optional[HostStager] = None) -> Tuple[StepBatch, Optional[torch.Tensor]]:
     """``pieces[i] = (slot, tokens, first_position)``: one device upload for all row metadata."""
     nseq = len(pieces)
     rows = sum(len(t) for _, t, _ in pieces)
     nw = 0 if want_rows is None else len(want_rows)
-    buf = np.empty(3 * rows + 4 * nseq + nw, dtype=np.int32)
+    total = 3 * rows + 4 * nseq + nw
+    state = {}
+
+    def fill(buf):
+        state["max"] = _fill_batch(buf, pieces, rows, nseq, nw, want_rows)
+    if stager is not None:
+        dev = stager.upload(total, fill)
+    else:
+        host = np.empty(total, dtype=np.int32)
+        fill(host)
+        dev = torch.from_numpy(host).to(device)
+    max_q, max_kv = state["max"]
+    o = 3 * rows
+    o2 = o + 4 * nseq
+    batch = StepBatch(rows=rows, nseq=nseq, max_q_len=max_q, max_kv_len=max_kv, ids=dev[:rows],
+                      row_pos=dev[rows:2 * rows], row_seq=dev[2 * rows:3 * rows],
+                      seq_slot=dev[o:o + nseq], seq_q_start=dev[o + nseq:o + 2 * nseq],
+                      seq_q_len=dev[o + 2 * nseq:o + 3 * nseq], seq_kv_len=dev[o + 3 * nseq:o2],
+                      device=torch.device(device), sm_count=sm_count)
+    return batch, (dev[o2:] if nw else None)
+
+
+def _fill_batch(buf, pieces, rows, nseq, nw, want_rows):
     ids, row_pos, row_seq = buf[:rows], buf[rows:2 * rows], buf[2 * rows:3 * rows]
     o = 3 * rows
     seq_slot, q_start, q_len, kv_len = (buf[o + i * nseq:o + (i + 1) * nseq] for i in range(4))
@@ -93,14 +148,7 @@ def build_batch(pieces: Sequence[Tuple[int, Sequence[int], int]], device, sm_cou
         r += n
     if nw:
         buf[o + 4 * nseq:] = want_rows
-    dev = torch.from_numpy(buf).to(device)
-    o2 = o + 4 * nseq
-    batch = StepBatch(rows=rows, nseq=nseq, max_q_len=max_q, max_kv_len=max_kv, ids=dev[:rows],
-                      row_pos=dev[rows:2 * rows], row_seq=dev[2 * rows:3 * rows],
-                      seq_slot=dev[o:o + nseq], seq_q_start=dev[o + nseq:o + 2 * nseq],
-                      seq_q_len=dev[o + 2 * nseq:o + 3 * nseq], seq_kv_len=dev[o + 3 * nseq:o2],
-                      device=torch.device(device), sm_count=sm_count)
-    return batch, (dev[o2:] if nw else None)
+    return max_q, max_kv
 
 
 class Engine:
@@ -115,6 +163,7 @@ class Engine:
         self.max_rows_per_pass = max_rows_per_pass
         self.vocab = model.spec.vocab
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.stager = HostStager(self.device)
         self.passes = 0
 
     # ---- slots ---------------------------------------------------------------------------
@@ -187,7 +236,8 @@ class Engine:
         return logits
 
     def _pass(self, pieces, want_rows: Sequence[int]) -> Optional[torch.Tensor]:
-        batch, want_dev = build_batch(pieces, self.device, self.sm_count, want_rows if want_rows else None)
+        batch, want_dev = build_batch(pieces, self.device, self.sm_count, want_rows if want_rows else None,
+                                      self.stager)
         self.passes += 1
         return self.model.forward(batch, self.cache, want_dev)
 

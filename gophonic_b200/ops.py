@@ -47,9 +47,14 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
-def _check(rc: int) -> None:
+launches = 0  # kernels launched through this module since import (a call that launches two counts two)
+
+
+def _check(rc: int, kernels: int = 1) -> None:
+    global launches
     if rc != 0:
         raise KernelError(_lib.gb_last_error().decode("utf-8", "replace"))
+    launches += kernels
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, dim=None, contiguous=True) -> None:
@@ -147,8 +152,15 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     kernels refuse, goes to the fp32 CUDA-core kernel.  float32 operands never touch a tensor
     core.
     """
+    _need(a, "gemm a", dim=2, contiguous=False)
+    _need(w, "gemm w", dim=2)
+    _need(out, "gemm out", dim=2, contiguous=False)
     M, K = a.shape
     N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"gemm: output dtype {out.dtype}")
     if algo == "simt" or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         gemm_simt(a, w, out)
         return "simt"
@@ -292,10 +304,11 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
                 algo = "decode_mma"
             elif max_q_len > 1 and _has("gb_attention_prefill_mma"):
                 algo = "prefill_mma"
+    nk = 2 if num_splits > 1 else 1
     if algo == "simt":
-        _check(_lib.gb_attention_simt(byref(p), _code(q.dtype), _stream()))
+        _check(_lib.gb_attention_simt(byref(p), _code(q.dtype), _stream()), nk)
     elif algo == "decode_mma":
-        _check(_lib.gb_attention_decode_mma(byref(p), _stream()))
+        _check(_lib.gb_attention_decode_mma(byref(p), _stream()), nk)
     elif algo == "prefill_mma":
         _check(_lib.gb_attention_prefill_mma(byref(p), _stream()))
     else:

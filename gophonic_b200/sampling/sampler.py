@@ -40,7 +40,11 @@ class DeviceSampler:
             self.seen[row].zero_()
 
     def select(self, logits: torch.Tensor, rows: Sequence[int]) -> List[int]:
-        """One token for each live row; ``logits[i]`` belongs to batch row ``rows[i]``."""
+        """One token for each live row, on the host; ``logits[i]`` belongs to batch row ``rows[i]``."""
+        return self.select_device(logits, rows).tolist()
+
+    def select_device(self, logits: torch.Tensor, rows: Sequence[int]) -> torch.Tensor:
+        """The same, left on the device as int32."""
         n = len(rows)
         opts = [self._opts[r] for r in rows]
         out = torch.empty(n, dtype=torch.int32, device=self.device)
@@ -67,4 +71,4 @@ class DeviceSampler:
             self.ops.mark_seen(out, self.vocab, self.seen, rows_dev)
         for r in rows:
             self._draws[r] += 1
-        return out.tolist()
+        return out
