@@ -273,6 +273,18 @@ int launch(const AttnParams& p, cudaStream_t stream) {
 
 }  // namespace
 
+// Merge of per-split partial results, shared with the tensor-core single-token kernel.
+int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
+                              int nseq, int heads, int d, int num_splits, cudaStream_t stream) {
+    if (dtype == GB_F32)
+        attn_merge_kernel<float><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (float*)out, out_row_stride, seq_q_start, heads, d, num_splits);
+    else
+        attn_merge_kernel<__nv_bfloat16><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (__nv_bfloat16*)out, out_row_stride,
+                                                                                seq_q_start, heads, d, num_splits);
+    GB_CHECK_LAUNCH("attention_merge");
+    return 0;
+}
+
 GB_API int gb_attention_simt(const AttnParams* pp, int dtype, cudaStream_t stream) {
     AttnParams p = *pp;
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;

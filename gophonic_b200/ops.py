@@ -299,7 +299,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr())
     if algo == "auto":
         algo = "simt"
-        if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256:
+        if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and (head_dim <= 128 or head_dim == 256) and ring_pages == 0:
             if max_q_len == 1 and _has("gb_attention_decode_mma"):
                 algo = "decode_mma"
             elif max_q_len > 1 and _has("gb_attention_prefill_mma"):

@@ -269,21 +269,38 @@ GEOMS = [(4, 2, 16), (6, 3, 32), (5, 1, 48), (8, 8, 64), (7, 1, 80), (4, 1, 96),
          (2, 2, 256)]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+KINDS = [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "auto")]
+
+
+@pytest.mark.parametrize("dtype,algo", KINDS)
 @pytest.mark.parametrize("heads,kvh,d", GEOMS)
-def test_attention_prompts(ops, dtype, heads, kvh, d):
+def test_attention_prompts(ops, dtype, algo, heads, kvh, d):
     """Whole prompts, prompts that continue a cached prefix, and a single row, in one batch."""
-    out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens=[70, 5, 1, 33], kv_lens=[70, 69, 130, 33])
+    out, ref, used = attention_case(ops, dtype, heads, kvh, d, q_lens=[70, 5, 1, 33], kv_lens=[70, 69, 130, 33], algo=algo)
+    close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+    if algo == "auto":
+        assert used == "prefill_mma"
+    out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens=[200, 130], kv_lens=[200, 333], algo=algo, seed=3)
     close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,algo", KINDS)
 @pytest.mark.parametrize("heads,kvh,d", GEOMS)
 @pytest.mark.parametrize("splits", [1, 3, 8])
-def test_attention_single_tokens(ops, dtype, heads, kvh, d, splits):
-    out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens=[1, 1, 1, 1, 1], kv_lens=[1, 64, 65, 700, 333],
-                                 splits=splits)
+def test_attention_single_tokens(ops, dtype, algo, heads, kvh, d, splits):
+    out, ref, used = attention_case(ops, dtype, heads, kvh, d, q_lens=[1, 1, 1, 1, 1], kv_lens=[1, 64, 65, 700, 333],
+                                    splits=splits, algo=algo)
     close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+    if algo == "auto":
+        assert used == "decode_mma"
+
+
+def test_attention_head_sizes_without_a_tensor_core_kernel_fall_back(ops):
+    out, ref, used = attention_case(ops, torch.bfloat16, 2, 1, 144, q_lens=[40, 1], kv_lens=[40, 90])
+    assert used == "simt"
+    close(out, ref, 1.2e-2)
+    with pytest.raises(ops.KernelError, match="head_dim 144"):
+        attention_case(ops, torch.bfloat16, 2, 1, 144, q_lens=[40], kv_lens=[40], algo="prefill_mma")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -308,8 +325,8 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, algo):
         assert ref[q_lens[0] - 1].abs().max() > 0
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_window_edge(ops, dtype):
+@pytest.mark.parametrize("dtype,algo", KINDS)
+def test_attention_window_edge(ops, dtype, algo):
     """With a window of w the key at distance w - 1 is the last one seen: a dominant key placed
     exactly there is found, one step further it is not."""
     heads, kvh, d, w = 2, 1, 32, 70
@@ -322,7 +339,7 @@ def test_attention_window_edge(ops, dtype):
             k_plane[page, :, off, 5] = 40.0
             q[:] = q * 0.05
             q[:, 5::d] = 40.0
-        out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, window=w, craft=craft)
+        out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, window=w, craft=craft, algo=algo)
         close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
 
 
