@@ -1,0 +1,318 @@
+// C[M, N] = A[M, K] * W[N, K]^T, bfloat16 operands, on the fifth-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands brought into shared memory by TMA.
+//
+// One CTA computes a 128 x 256 tile.  Roles, by warp:
+//   warp 0   one lane issues the TMA loads (cp.async.bulk.tensor.2d) of a 128 x 64 slab of A and a
+//            256 x 64 slab of W per stage into 128-byte-swizzled shared memory, four stages deep;
+//   warp 1   allocates 256 columns of tensor memory; one lane issues four tcgen05.mma
+//            (M 128, N 256, K 16) per stage and commits the stage's barrier when they are done;
+//   warps 2-5  wait for the last commit, read the accumulator with tcgen05.ld (each warp the 32
+//            lanes of its quadrant), convert and store 32 columns at a time.
+// CTAs are numbered with the M tile fastest, so the CTAs that run together share their W slabs
+// and W crosses HBM once.  Edges: TMA fills rows and columns outside the operands with zeros and
+// the stores are bounded, so M, N and K need no padding (K and the row strides must be multiples
+// of 8 elements, the 16-byte rule of TMA).
+//
+// Every wait on a barrier gives up after a bounded number of polls; the CTA then records a status
+// word, lets its roles run out, frees its tensor memory and returns.  The status is read with
+// gb_gemm_tc5_status().
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 256;
+constexpr int THREADS = 192;
+constexpr unsigned SPIN_LIMIT = 1u << 24;
+
+__device__ int g_tc5_status;  // 0, or the code of the first wait that gave up
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+// true when the phase with this parity has completed; false after SPIN_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done = 0;
+    for (unsigned i = 0; i < SPIN_LIMIT; i++) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(s32(bar)), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(s32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(s32(bar))
+        : "memory");
+}
+
+// K-major operand tile in 128-byte-swizzled shared memory: rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with this swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows * 128 bytes
+    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major
+__device__ __forceinline__ uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <typename TC>
+__global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                          const __grid_constant__ CUtensorMap map_w, TC* __restrict__ C, int M, int N,
+                                                          int K, int64_t ldc) {
+    extern __shared__ unsigned char smem_raw[];
+    // operand stages need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int KT = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < KT; kt++) {
+                const int s = kt % STAGES;
+                const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+                    atomicCAS(&g_tc5_status, 0, 1);
+                    abort_s = 1;
+                    break;
+                }
+                if (*(volatile int*)&abort_s) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                tma_load_2d(st, &map_a, kt * BK, m0, &full_bar[s]);
+                tma_load_2d(st + A_BYTES, &map_w, kt * BK, n0, &full_bar[s]);
+                issued = kt + 1;
+            }
+            if (*(volatile int*)&abort_s) {
+                // let the copies that are still in flight land before the CTA leaves
+                for (int kt = issued > STAGES ? issued - STAGES : 0; kt < issued; kt++)
+                    mbar_wait(&full_bar[kt % STAGES], (uint32_t)(kt / STAGES) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(BM, BN);
+            bool ok = true;
+            for (int kt = 0; kt < KT; kt++) {
+                const int s = kt % STAGES;
+                const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
+                if (!mbar_wait(&full_bar[s], phase)) {
+                    atomicCAS(&g_tc5_status, 0, 2);
+                    abort_s = 1;
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t a_addr = s32(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++) {
+                    // 16 elements of K = 32 bytes = 2 units of the descriptor's address field
+                    umma(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);  // the stage is free once these products have read it
+            }
+            if (ok) umma_commit(&accum_bar);
+        }
+    } else {
+        // epilogue: warp w reads the tensor-memory lanes of quadrant w % 4
+        const int quad = warp & 3;
+        const int row = m0 + quad * 32 + lane;
+        if (mbar_wait(&accum_bar, 0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N) break;  // uniform across the warp
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+                if (row < M) {
+                    TC* dst = C + (int64_t)row * ldc + n0 + c0;
+                    if (vec_ok && n0 + c0 + 32 <= N) {
+                        if (sizeof(TC) == 2) {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                uint4 v;
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
+                                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
+                                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
+                                v.x = *reinterpret_cast<uint32_t*>(&t0);
+                                v.y = *reinterpret_cast<uint32_t*>(&t1);
+                                v.z = *reinterpret_cast<uint32_t*>(&t2);
+                                v.w = *reinterpret_cast<uint32_t*>(&t3);
+                                d4[i] = v;
+                            }
+                        } else {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int i = 0; i < 8; i++) d4[i] = make_uint4(r[i * 4], r[i * 4 + 1], r[i * 4 + 2], r[i * 4 + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (n0 + c0 + i < N) dst[i] = from_f32<TC>(__uint_as_float(r[i]));
+                    }
+                }
+            }
+        } else {
+            atomicCAS(&g_tc5_status, 0, 3);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x K bf16, K contiguous, row stride ld elements; box of box_rows x 64
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) GB_REFUSE("gemm_tc5: the driver offers no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) GB_REFUSE("gemm_tc5: cuTensorMapEncodeTiled failed with code %d (rows %d, K %d, stride %lld)", (int)r, rows, K, (long long)ld);
+    return 0;
+}
+
+template <typename TC>
+int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream) {
+    const int smem = STAGES * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) GB_REFUSE("gemm_tc5: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_a, map_w;
+    if (int rc = make_map(&map_a, A, M, K, lda, BM)) return rc;
+    if (int rc = make_map(&map_w, W, N, K, K, BN)) return rc;
+    dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
+    if (grid.y > 65535) GB_REFUSE("gemm_tc5: N = %d exceeds one launch", N);
+    gemm_tc5_kernel<TC><<<grid, THREADS, smem, stream>>>(map_a, map_w, (TC*)C, M, N, K, ldc);
+    GB_CHECK_LAUNCH("gemm_tc5");
+    return 0;
+}
+
+}  // namespace
+
+GB_API int gb_gemm_tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
+                       cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5: K = %d must be a positive multiple of 8", K);
+    if ((lda & 7) || lda < K) GB_REFUSE("gemm_tc5: row stride %lld of A must be a multiple of 8 and at least K", (long long)lda);
+    if (ldc < N) GB_REFUSE("gemm_tc5: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5: operands must be 16-byte aligned");
+    if (c_dtype == GB_F32) return launch<float>(A, W, C, M, N, K, lda, ldc, stream);
+    if (c_dtype == GB_BF16) return launch<__nv_bfloat16>(A, W, C, M, N, K, lda, ldc, stream);
+    GB_REFUSE("gemm_tc5: unknown output dtype %d", c_dtype);
+}
+
+// 0 if no tcgen05 kernel has given up on a barrier since the last call; else the role that did
+// (1 loader, 2 multiplier, 3 epilogue).  Synchronises the device.
+GB_API int gb_gemm_tc5_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc5_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_tc5_status, &zero, sizeof(int));
+    return v;
+}

@@ -195,9 +195,16 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
 
 
 def tc5_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes this product (TMA wants 16-byte rows; edges are free)."""
     K = a.shape[1]
-    N = w.shape[0]
-    return (K % 64 == 0 and N % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)
+    return K % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def tc5_status() -> int:
+    """0, or which role of a tcgen05 kernel gave up waiting on a barrier since the last call."""
+    if not _has("gb_gemm_tc5_status"):
+        return 0
+    return int(_lib.gb_gemm_tc5_status())
 
 
 # ---- attention ---------------------------------------------------------------------------
