@@ -174,6 +174,7 @@ class TokenGenerator:
         from .engine.generate import Generator
         g = Generator(self.engine, self.sampler, self.batch, self.context, stop_ids)
         out = g.generate(prompts, options, on_token)
+        self.engine.check_kernels()
         self.stats = g.stats
         return out
 

@@ -176,6 +176,12 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def check_kernels(self) -> None:
+        """Raise if a kernel recorded that it gave up waiting on a barrier (synchronises)."""
+        code = self.model.rt.ops.tc5_status()
+        if code:
+            raise RuntimeError(f"a tcgen05 kernel gave up waiting on a barrier (role {code}); results are not valid")
+
     def room(self) -> int:
         """Free pages of 64 tokens."""
         return self.cache.pages.available()

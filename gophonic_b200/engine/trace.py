@@ -62,6 +62,7 @@ def main(argv=None) -> int:
             for rid in fresh:  # a refused step leaves nothing behind
                 engine.end_sequence(slots.pop(rid))
             raise
+        engine.check_kernels()
         if logits is not None and logits.numel() > 0:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
             arr.tofile(os.path.join(args.out, f"{step}.f32"))
