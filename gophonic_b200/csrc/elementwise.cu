@@ -92,10 +92,91 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
     }
 }
 
+// The same operation for rows whose width is a multiple of 4 and at most THREADS * 16: every
+// thread keeps its (up to four) float4 pieces of the row in registers, so the row is read once.
+template <typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS) add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                                  const float* __restrict__ w, float eps, int n, TO* __restrict__ out,
+                                                                  const int* __restrict__ row_index) {
+    __shared__ float warp_part[THREADS / 32];
+    __shared__ float inv_s;
+    const int orow = blockIdx.x;
+    const int row = row_index ? row_index[orow] : orow;
+    float4* hr = reinterpret_cast<float4*>(h + (int64_t)row * n);
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + (int64_t)row * n) : nullptr;
+    const bool write_back = (row_index == nullptr) && (delta != nullptr);
+    const int n4 = n >> 2;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int c = threadIdx.x + i * THREADS;
+        if (c < n4) {
+            v[i] = hr[c];
+            if (dr) {
+                float4 d = dr[c];
+                v[i].x += d.x;
+                v[i].y += d.y;
+                v[i].z += d.z;
+                v[i].w += d.w;
+            }
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < THREADS / 32; i++) t += warp_part[i];
+        inv_s = 1.0f / sqrtf(t / (float)n + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    TO* orow_p = out + (int64_t)orow * n;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int c = threadIdx.x + i * THREADS;
+        if (c < n4) {
+            if (write_back) hr[c] = v[i];
+            float4 ww = w4[c];
+            float a = v[i].x * inv * ww.x, b = v[i].y * inv * ww.y, cc = v[i].z * inv * ww.z, d = v[i].w * inv * ww.w;
+            if (sizeof(TO) == 4) {
+                reinterpret_cast<float4*>(orow_p)[c] = make_float4(a, b, cc, d);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(cc, d);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(orow_p)[c] = pk;
+            }
+        }
+    }
+}
+
 GB_API int gb_add_rmsnorm(float* h, const float* delta, const float* w, float eps, int n, void* out, int out_dtype,
                           const int* row_index, int out_rows, cudaStream_t stream) {
     if (out_rows <= 0) return 0;
     if (n <= 0) GB_REFUSE("add_rmsnorm: width %d", n);
+    if (out_dtype != GB_F32 && out_dtype != GB_BF16) GB_REFUSE("add_rmsnorm: unknown output dtype %d", out_dtype);
+    const bool aligned = !(((uintptr_t)h | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15);
+    if ((n & 3) == 0 && n <= 1024 * 16 && aligned) {
+        if (n <= 256 * 16) {
+            if (out_dtype == GB_F32)
+                add_rmsnorm_vec_kernel<float, 256><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (float*)out, row_index);
+            else
+                add_rmsnorm_vec_kernel<__nv_bfloat16, 256><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
+        } else {
+            if (out_dtype == GB_F32)
+                add_rmsnorm_vec_kernel<float, 1024><<<out_rows, 1024, 0, stream>>>(h, delta, w, eps, n, (float*)out, row_index);
+            else
+                add_rmsnorm_vec_kernel<__nv_bfloat16, 1024><<<out_rows, 1024, 0, stream>>>(h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
+        }
+        GB_CHECK_LAUNCH("add_rmsnorm");
+        return 0;
+    }
     if (out_dtype == GB_F32)
         add_rmsnorm_kernel<float><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (float*)out, row_index);
     else if (out_dtype == GB_BF16)

@@ -13,10 +13,11 @@
 
 namespace {
 
-constexpr int MAX_KW = 8;
+int g_max_kw = 0;      // most warps that split K inside a CTA (0: chosen by shape)
+int g_min_steps = 4;   // fewest 32-wide K steps a warp should own
 
 template <int MT>  // MT tiles of 8 batch rows
-__global__ void __launch_bounds__(256) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
+__global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                                                          void* __restrict__ Yv, int y_is_bf16, int M, int N, int K, int64_t ldx,
                                                          int64_t ldy, int k_per_warp) {
     extern __shared__ float red[];  // [KW][16][MT * 8]
@@ -97,8 +98,11 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const __nv_bfloat16* _
 template <int MT>
 int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, cudaStream_t stream) {
     int steps = ceil_div(K, 32);
+    // Few weight tiles (narrow outputs) leave SMs short of loads in flight: give each CTA more warps.
+    int max_kw = g_max_kw;
+    if (max_kw == 0) max_kw = (ceil_div(N, 16) <= 320 && MT <= 4) ? 16 : 8;
     int kw = 1;
-    while (kw < MAX_KW && steps / (kw * 2) >= 4) kw *= 2;  // at least four 32-wide steps per warp
+    while (kw < max_kw && steps / (kw * 2) >= g_min_steps) kw *= 2;
     int k_per_warp = ceil_div(steps, kw) * 32;
     size_t smem = (size_t)kw * 16 * MT * 8 * sizeof(float);
     gemm_skinny_kernel<MT><<<ceil_div(N, 16), kw * 32, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, Y,
@@ -108,6 +112,15 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
 }
 
 }  // namespace
+
+// Tuning knobs for measurements: most K-splitting warps per CTA (a power of two, at most 16) and the
+// fewest 32-wide steps a warp should own.
+GB_API int gb_gemm_skinny_tune(int max_kw, int min_steps) {
+    if (max_kw < 0 || max_kw > 16 || (max_kw & (max_kw - 1)) || min_steps < 1) GB_REFUSE("gemm_skinny_tune: (%d, %d)", max_kw, min_steps);
+    g_max_kw = max_kw;
+    g_min_steps = min_steps;
+    return 0;
+}
 
 GB_API int gb_gemm_skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
                           cudaStream_t stream) {

@@ -89,6 +89,76 @@ __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ lo
     if (threadIdx.x == 0) out[r] = t;
 }
 
+// Two-stage argmax for wide rows: a CTA per (row, chunk of 8192 logits) leaves its best (value,
+// index) in scratch, then one CTA per row takes the first maximum of the chunk results.
+constexpr int ARG_CHUNK = 8192;
+
+__global__ void __launch_bounds__(256) argmax_part_kernel(const float* __restrict__ logits, int vocab, int64_t stride,
+                                                          float* __restrict__ part_val, int* __restrict__ part_idx, int chunks) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    const int r = blockIdx.y, c = blockIdx.x;
+    const float* row = logits + (int64_t)r * stride;
+    const int lo = c * ARG_CHUNK, hi = lo + ARG_CHUNK < vocab ? lo + ARG_CHUNK : vocab;
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += 256) {
+        float v = row[i];
+        if (v > best) {
+            best = v;
+            at = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > best || (ov == best && oi < at)) {
+            best = ov;
+            at = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        s_val[threadIdx.x >> 5] = best;
+        s_idx[threadIdx.x >> 5] = at;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++)
+            if (s_val[w] > best || (s_val[w] == best && s_idx[w] < at)) {
+                best = s_val[w];
+                at = s_idx[w];
+            }
+        part_val[(int64_t)r * chunks + c] = best;
+        part_idx[(int64_t)r * chunks + c] = at;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
+                                    int* __restrict__ out) {
+    const int r = blockIdx.x;
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int c = threadIdx.x; c < chunks; c += 32) {
+        float v = part_val[(int64_t)r * chunks + c];
+        int i = part_idx[(int64_t)r * chunks + c];
+        if (v > best || (v == best && i < at)) {
+            best = v;
+            at = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > best || (ov == best && oi < at)) {
+            best = ov;
+            at = oi;
+        }
+    }
+    if (threadIdx.x == 0) out[r] = at == 0x7fffffff ? 0 : at;
+}
+
 // exclusive prefix sum of one unsigned per thread over the CTA, in thread order
 __device__ __forceinline__ uint32_t block_scan_u32(uint32_t v, uint32_t* part, uint32_t* total) {
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -286,6 +356,22 @@ GB_API int gb_argmax(const float* logits, int rows, int vocab, int64_t stride, i
     if (vocab <= 0 || stride < vocab) GB_REFUSE("argmax: vocab %d, stride %lld", vocab, (long long)stride);
     argmax_kernel<<<rows, ST, 0, stream>>>(logits, vocab, stride, out);
     GB_CHECK_LAUNCH("argmax");
+    return 0;
+}
+
+// scratch: rows * ceil(vocab / 8192) floats followed by as many ints
+GB_API int gb_argmax_wide(const float* logits, int rows, int vocab, int64_t stride, int* out, void* scratch, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || stride < vocab) GB_REFUSE("argmax: vocab %d, stride %lld", vocab, (long long)stride);
+    if (rows > 65535) GB_REFUSE("argmax: %d rows exceed one launch", rows);
+    if (!scratch) GB_REFUSE("argmax: the two-stage kernel needs scratch");
+    const int chunks = ceil_div(vocab, ARG_CHUNK);
+    float* pv = (float*)scratch;
+    int* pi = (int*)(pv + (int64_t)rows * chunks);
+    argmax_part_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, stride, pv, pi, chunks);
+    GB_CHECK_LAUNCH("argmax_part");
+    argmax_final_kernel<<<rows, 32, 0, stream>>>(pv, pi, chunks, out);
+    GB_CHECK_LAUNCH("argmax_final");
     return 0;
 }
 

@@ -103,6 +103,11 @@ class Model:
             b.mixer.prepare(capacity)
         return cache
 
+    @property
+    def capturable(self) -> bool:
+        """Whether every part only enqueues stream work, so a step can be captured in a CUDA graph."""
+        return all(b.capturable for b in self.blocks) and self.final_norm.capturable
+
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights a step reads once: every layer run's matrices and the head."""
         total = self.head.numel() * self.head.element_size()

@@ -86,6 +86,13 @@ class HostStager:
 
     def upload(self, n: int, fill) -> torch.Tensor:
         """A device int32 tensor of ``n`` elements whose contents ``fill(numpy_view)`` writes."""
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        self.upload_into(dev, fill)
+        return dev
+
+    def upload_into(self, dev: torch.Tensor, fill) -> None:
+        """Fill the device int32 tensor ``dev`` with what ``fill(numpy_view)`` writes."""
+        n = dev.numel()
         i = self.at
         self.at = (self.at + 1) % self.ring
         if self.events[i] is not None:
@@ -94,13 +101,11 @@ class HostStager:
             self.bufs[i] = torch.empty(max(1024, 2 * n), dtype=torch.int32).pin_memory()
         host = self.bufs[i][:n]
         fill(host.numpy())
-        dev = torch.empty(n, dtype=torch.int32, device=self.device)
         dev.copy_(host, non_blocking=True)
         if self.events[i] is None:
             self.events[i] = torch.cuda.Event()
         self.events[i].record()
         self.bytes_uploaded += 4 * n
-        return dev
 
 
 def build_batch(pieces: Sequence[Tuple[int, Sequence[int], int]], device, sm_count: int = 148,
@@ -155,7 +160,8 @@ class Engine:
     """A model, its cache and the step function over them."""
 
     def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
-                 max_seq_tokens: Optional[int] = None, max_rows_per_pass: int = 16384):
+                 max_seq_tokens: Optional[int] = None, max_rows_per_pass: int = 16384, use_graphs: bool = True,
+                 max_graph_batch: int = 64):
         self.model = model
         self.device = model.rt.device
         self.cache: Cache = model.new_cache(max_tokens, max_slots, max_seq_tokens)
@@ -165,6 +171,12 @@ class Engine:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.stager = HostStager(self.device)
         self.passes = 0
+        self.graphs = None
+        if use_graphs and model.capturable:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self, max_graph_batch)
+        # kv heads of the widest attention group: how many CTAs a sequence gives single-token attention
+        self._kv_heads_hint = max([g["kv_heads"] for g in self.cache.groups() if g["kind"] == "kv"] or [1])
 
     # ---- slots ---------------------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -233,7 +245,11 @@ class Engine:
         total_rows = r
         want_rows = [starts[i] + int(w) for i in range(len(entries)) for w in want[i]]
 
-        if total_rows <= self.max_rows_per_pass:
+        single = total_rows == len(entries)
+        if (single and self.graphs is not None and total_rows <= self.graphs.max_batch
+                and want_rows == list(range(total_rows))):
+            logits = self._graph_pass(entries)
+        elif total_rows <= self.max_rows_per_pass:
             pieces = [(slot, list(toks), self.cache.length(slot)) for slot, toks in entries]
             logits = self._pass(pieces, want_rows)
         else:
@@ -246,6 +262,35 @@ class Engine:
                                       self.stager)
         self.passes += 1
         return self.model.forward(batch, self.cache, want_dev)
+
+    def _graph_pass(self, entries) -> torch.Tensor:
+        """One token each, every row wanted: replay the captured step."""
+        n = len(entries)
+        firsts = [self.cache.length(slot) for slot, _ in entries]
+        g = self.graphs.get(n, max(firsts) + 1, self._kv_heads_hint)
+        if g.logits is None:
+            # the capture runs the step's kernels on the graph's own input buffer: fill it first
+            self._fill_graph_meta(g, entries, firsts)
+            torch.cuda.synchronize()
+            g.capture()
+        self._fill_graph_meta(g, entries, firsts)
+        self.passes += 1
+        return g.replay()
+
+    def _fill_graph_meta(self, g, entries, firsts) -> None:
+        n = len(entries)
+
+        def fill(buf):
+            for i, ((slot, toks), first) in enumerate(zip(entries, firsts)):
+                buf[i] = toks[0]
+                buf[n + i] = first
+                buf[2 * n + i] = i
+                buf[3 * n + i] = slot
+                buf[4 * n + i] = i
+                buf[5 * n + i] = 1
+                buf[6 * n + i] = first + 1
+                buf[7 * n + i] = i
+        self.stager.upload_into(g.meta, fill)
 
     def _chunked(self, entries, starts, want_rows) -> Optional[torch.Tensor]:
         """Cut the packed rows into passes of at most ``max_rows_per_pass`` rows."""

@@ -329,8 +329,14 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _need(out, "argmax out", torch.int32, 1)
     if logits.stride(1) != 1 or out.numel() != logits.shape[0]:
         raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {out.numel()}")
-    _check(_lib.gb_argmax(_ptr(logits), c_int(logits.shape[0]), c_int(logits.shape[1]), c_int64(logits.stride(0)),
-                          _ptr(out), _stream()))
+    rows, vocab = logits.shape
+    if vocab > 16384:  # wide rows: many CTAs a row, merged by a second small kernel
+        chunks = (vocab + 8191) // 8192
+        scratch = torch.empty(2 * rows * chunks, dtype=torch.float32, device=logits.device)
+        _check(_lib.gb_argmax_wide(_ptr(logits), c_int(rows), c_int(vocab), c_int64(logits.stride(0)), _ptr(out),
+                                   _ptr(scratch), _stream()), 2)
+        return
+    _check(_lib.gb_argmax(_ptr(logits), c_int(rows), c_int(vocab), c_int64(logits.stride(0)), _ptr(out), _stream()))
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

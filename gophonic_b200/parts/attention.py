@@ -20,6 +20,8 @@ from .base import KVRequest, Mixer, Runtime, TensorDecl
 
 
 class Attention(Mixer):
+    capturable = True
+
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
         qd, kvd = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim

@@ -69,6 +69,10 @@ class Runtime:
 
 class Part:
     category = ""
+    # True if forward only enqueues work on the current CUDA stream (no host reads of device data,
+    # no fresh host-side state): such a part may be captured into a CUDA graph.  The default is the
+    # safe one; the engine replays single-token steps from graphs only if every part says True.
+    capturable = False
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:

@@ -44,6 +44,10 @@ class PreNormBlock(Part):
         self.feed_forward = registry.part_class("feed_forward", layer.feed_forward.kind)(
             layer.feed_forward, p + layer.feed_forward_prefix, tensors, runtime)
 
+    @property
+    def capturable(self) -> bool:
+        return all(p.capturable for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward))
+
     def forward(self, batch, h: torch.Tensor, delta: Optional[torch.Tensor], cache) -> torch.Tensor:
         """Runs the layer on residual ``h`` (fp32, updated in place) with the pending addend
         ``delta``; returns the new pending addend."""

@@ -11,6 +11,8 @@ from .base import Norm, Runtime, TensorDecl
 
 
 class RMSNorm(Norm):
+    capturable = True
+
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
         return [TensorDecl(prefix + "weight", (spec.size,), role="norm")]

@@ -11,6 +11,8 @@ from .base import FeedForward, Runtime, TensorDecl
 
 
 class SwiGLU(FeedForward):
+    capturable = True
+
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
         return [TensorDecl(prefix + "gate_proj.weight", (spec.intermediate, spec.hidden)),

@@ -207,6 +207,40 @@ def test_prompt_fed_in_pieces_and_in_row_chunks(model_dirs, references, plain_mo
     assert rel_err(got, references("B", t)) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_graph_steps_equal_eager_steps(model_dirs, plain_models, dtype):
+    """Single-token steps are replayed from a CUDA graph; they must give the eager step's logits bit
+    for bit, across batch sizes, growing contexts (the key-split count changes) and slot reuse."""
+    from gophonic_b200.engine import Engine, Model
+    cfg, _ = plain_models["B"]
+    model = Model.from_dir(model_dirs["B"], dtype=dtype)
+    eager = Engine(model, max_tokens=4096, use_graphs=False)
+    graph = Engine(model, max_tokens=4096, use_graphs=True)
+    assert eager.graphs is None and graph.graphs is not None
+    rng = np.random.default_rng(7)
+
+    def run(eng, prompts, toks):
+        slots = [eng.new_sequence() for _ in prompts]
+        got = [eng.step(list(zip(slots, prompts))).cpu().numpy()]
+        live = list(range(len(prompts)))
+        for s in range(toks.shape[0]):
+            if s == 20:
+                eng.end_sequence(slots[live.pop(1)])  # one request ends earlier: the batch shrinks
+            got.append(eng.step([(slots[i], [int(toks[s, i])]) for i in live]).cpu().numpy())
+        for i in live:
+            eng.end_sequence(slots[i])
+        return got
+
+    for lens in ([300, 5, 64, 1], [700, 2, 130]):
+        prompts = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lens]
+        toks = rng.integers(0, cfg["vocab_size"], size=(40, len(prompts)))
+        a, b = run(eager, prompts, toks), run(graph, prompts, toks)
+        assert len(a) == len(b) == 41
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
+    assert len(graph.graphs.graphs) >= 3  # several batch sizes and split counts were captured
+
+
 def test_where_a_sequence_lies_in_the_cache_changes_nothing(engines, plain_models):
     eng = engines("A", "float32", 1024)
     cfg, _ = plain_models["A"]
