@@ -34,12 +34,13 @@ SOURCES = [
     "gemm_mma.cu",
     "gemm_skinny.cu",
     "gemm_tc5.cu",
+    "gemm_tc5_decode.cu",
     "attention_simt.cu",
     "attention_mma.cu",
     "sampling.cu",
     "no_alloc.cu",
 ]
-HEADERS = ["common.cuh", "mma.cuh", "no_alloc.h"]
+HEADERS = ["common.cuh", "mma.cuh", "tc5.cuh", "no_alloc.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -212,27 +212,32 @@ __device__ __forceinline__ float silu_f32(float x) {
     return x * e / (1.f + e);
 }
 
+// interleave8 = 0: gate in columns [0, I), up in [I, 2I).  interleave8 = 1: blocks of sixteen
+// columns, eight gate columns followed by the eight up columns of the same outputs.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int64_t gu_stride) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int64_t gu_stride, int interleave8) {
     int r = blockIdx.y;
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
     const T* g = gu + (int64_t)r * gu_stride;
-    float a = to_f32<T>(g[i]);
-    float b = to_f32<T>(g[inter + i]);
+    int gi = interleave8 ? ((i >> 3) << 4) + (i & 7) : i;
+    int ui = interleave8 ? gi + 8 : inter + i;
+    float a = to_f32<T>(g[gi]);
+    float b = to_f32<T>(g[ui]);
     out[(int64_t)r * inter + i] = from_f32<T>(silu_f32(a) * b);
 }
 
-GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, cudaStream_t stream) {
+GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, int interleave8, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (inter <= 0) GB_REFUSE("swiglu: width %d", inter);
+    if (interleave8 && (inter & 7)) GB_REFUSE("swiglu: interleaved columns need a width that is a multiple of 8, got %d", inter);
     if (rows > 65535) GB_REFUSE("swiglu: %d rows exceed one launch (65535); the step splits larger batches", rows);
     dim3 grid(ceil_div(inter, 256), rows);
     if (dtype == GB_F32)
-        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter);
+        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter, interleave8);
     else if (dtype == GB_BF16)
         swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter,
-                                                               2 * (int64_t)inter);
+                                                               2 * (int64_t)inter, interleave8);
     else
         GB_REFUSE("swiglu: unknown dtype %d", dtype);
     GB_CHECK_LAUNCH("swiglu");

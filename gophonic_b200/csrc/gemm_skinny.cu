@@ -19,7 +19,7 @@ int g_min_steps = 4;   // fewest 32-wide K steps a warp should own
 template <int MT>  // MT tiles of 8 batch rows
 __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                                                          void* __restrict__ Yv, int y_is_bf16, int M, int N, int K, int64_t ldx,
-                                                         int64_t ldy, int k_per_warp) {
+                                                         int64_t ldy, int k_per_warp, int epi) {
     extern __shared__ float red[];  // [KW][16][MT * 8]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, KW = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -83,6 +83,27 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
         mine[(g + 8) * MB + j * 8 + 2 * t + 1] = acc[j][3];
     }
     __syncthreads();
+    if (epi == 1) {
+        // rows 0-7 of the tile are gate rows and rows 8-15 the up rows of the same eight outputs:
+        // out[b, n0 / 2 + i] = silu(gate) * up            (internal/qwen3lm/gpu.metal:130-137)
+        for (int idx = threadIdx.x; idx < 8 * MB; idx += blockDim.x) {
+            int b = idx >> 3, i = idx & 7;
+            if (b >= M || n0 + 8 + i >= N) continue;
+            float gsum = 0.f, usum = 0.f;
+            for (int w = 0; w < KW; w++) {
+                gsum += red[(size_t)w * 16 * MB + i * MB + b];
+                usum += red[(size_t)w * 16 * MB + (i + 8) * MB + b];
+            }
+            float act = gsum >= 0.f ? gsum / (1.f + expf(-gsum)) : gsum * expf(gsum) / (1.f + expf(gsum));
+            act *= usum;
+            int64_t o = (int64_t)b * ldy + (n0 >> 1) + i;
+            if (y_is_bf16)
+                ((__nv_bfloat16*)Yv)[o] = __float2bfloat16_rn(act);
+            else
+                ((float*)Yv)[o] = act;
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < 16 * MB; idx += blockDim.x) {
         int b = idx >> 4, i = idx & 15;  // 16 consecutive outputs of one batch row
         if (b >= M || n0 + i >= N) continue;
@@ -96,7 +117,8 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
 }
 
 template <int MT>
-int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, cudaStream_t stream) {
+int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, int epi,
+           cudaStream_t stream) {
     int steps = ceil_div(K, 32);
     // Few weight tiles (narrow outputs) leave SMs short of loads in flight: give each CTA more warps.
     int max_kw = g_max_kw;
@@ -106,7 +128,7 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
     int k_per_warp = ceil_div(steps, kw) * 32;
     size_t smem = (size_t)kw * 16 * MT * 8 * sizeof(float);
     gemm_skinny_kernel<MT><<<ceil_div(N, 16), kw * 32, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, Y,
-                                                                      c_dtype == GB_BF16, M, N, K, ldx, ldy, k_per_warp);
+                                                                      c_dtype == GB_BF16, M, N, K, ldx, ldy, k_per_warp, epi);
     GB_CHECK_LAUNCH("gemm_skinny");
     return 0;
 }
@@ -122,17 +144,31 @@ GB_API int gb_gemm_skinny_tune(int max_kw, int min_steps) {
     return 0;
 }
 
-GB_API int gb_gemm_skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
-                          cudaStream_t stream) {
+static int skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, int epi,
+                  cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64) GB_REFUSE("gemm_skinny: %d rows; this kernel takes at most 64", M);
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_skinny: K = %d must be a positive multiple of 8", K);
     if ((ldx & 7) || ldx < K) GB_REFUSE("gemm_skinny: row stride %lld of X must be a multiple of 8 and at least K", (long long)ldx);
-    if (ldy < N) GB_REFUSE("gemm_skinny: row stride %lld of Y is shorter than N = %d", (long long)ldy, N);
+    if (epi == 0 && ldy < N) GB_REFUSE("gemm_skinny: row stride %lld of Y is shorter than N = %d", (long long)ldy, N);
+    if (epi == 1 && ((N & 15) || ldy < N / 2))
+        GB_REFUSE("gemm_skinny: the SwiGLU epilogue needs N = %d to be a multiple of 16 and Y rows of at least N / 2 (stride %lld)", N, (long long)ldy);
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (c_dtype != GB_F32 && c_dtype != GB_BF16) GB_REFUSE("gemm_skinny: unknown output dtype %d", c_dtype);
-    if (M <= 8) return launch<1>(X, W, Y, c_dtype, M, N, K, ldx, ldy, stream);
-    if (M <= 16) return launch<2>(X, W, Y, c_dtype, M, N, K, ldx, ldy, stream);
-    if (M <= 32) return launch<4>(X, W, Y, c_dtype, M, N, K, ldx, ldy, stream);
-    return launch<8>(X, W, Y, c_dtype, M, N, K, ldx, ldy, stream);
+    if (M <= 8) return launch<1>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
+    if (M <= 16) return launch<2>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
+    if (M <= 32) return launch<4>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
+    return launch<8>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
+}
+
+GB_API int gb_gemm_skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
+                          cudaStream_t stream) {
+    return skinny(X, W, Y, c_dtype, M, N, K, ldx, ldy, 0, stream);
+}
+
+// Y[M, N / 2] = silu(X Wg^T) * (X Wu^T) where W holds gate and up rows interleaved in blocks of
+// eight (rows 16j .. 16j+7 are gate rows 8j .. 8j+7, rows 16j+8 .. 16j+15 the matching up rows).
+GB_API int gb_gemm_skinny_swiglu(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx,
+                                 int64_t ldy, cudaStream_t stream) {
+    return skinny(X, W, Y, c_dtype, M, N, K, ldx, ldy, 1, stream);
 }

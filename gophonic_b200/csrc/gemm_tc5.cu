@@ -16,9 +16,9 @@
 // Every wait on a barrier gives up after a bounded number of polls; the CTA then records a status
 // word, lets its roles run out, frees its tensor memory and returns.  The status is read with
 // gb_gemm_tc5_status().
-#include "common.cuh"
+#include "tc5.cuh"
 
-#include <cuda.h>
+__device__ int g_tc5_status;
 
 namespace {
 
@@ -26,85 +26,7 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 256;
 constexpr int THREADS = 192;
-constexpr unsigned SPIN_LIMIT = 1u << 24;
 
-__device__ int g_tc5_status;  // 0, or the code of the first wait that gave up
-
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
-}
-// true when the phase with this parity has completed; false after SPIN_LIMIT polls
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t done = 0;
-    for (unsigned i = 0; i < SPIN_LIMIT; i++) {
-        asm volatile(
-            "{\n"
-            ".reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n"
-            "}\n"
-            : "=r"(done)
-            : "r"(s32(bar)), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(s32(smem_dst)),
-        "l"(map), "r"(x), "r"(y), "r"(s32(bar))
-        : "memory");
-}
-
-// K-major operand tile in 128-byte-swizzled shared memory: rows of 128 bytes, groups of 8 rows
-// 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);        // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with this swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows * 128 bytes
-    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
-    return d;
-}
-
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major
-__device__ __forceinline__ uint32_t instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(s32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
 
 template <typename TC>
 __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -243,38 +165,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// rows x K bf16, K contiguous, row stride ld elements; box of box_rows x 64
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) GB_REFUSE("gemm_tc5: the driver offers no cuTensorMapEncodeTiled");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) GB_REFUSE("gemm_tc5: cuTensorMapEncodeTiled failed with code %d (rows %d, K %d, stride %lld)", (int)r, rows, K, (long long)ld);
-    return 0;
-}
-
 template <typename TC>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream) {
     const int smem = STAGES * STAGE_BYTES + 1024;
@@ -285,8 +175,8 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
         configured = true;
     }
     CUtensorMap map_a, map_w;
-    if (int rc = make_map(&map_a, A, M, K, lda, BM)) return rc;
-    if (int rc = make_map(&map_w, W, N, K, K, BN)) return rc;
+    if (int rc = tc5_make_map(&map_a, A, M, K, lda, BM)) return rc;
+    if (int rc = tc5_make_map(&map_w, W, N, K, K, BN)) return rc;
     dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
     if (grid.y > 65535) GB_REFUSE("gemm_tc5: N = %d exceeds one launch", N);
     gemm_tc5_kernel<TC><<<grid, THREADS, smem, stream>>>(map_a, map_w, (TC*)C, M, N, K, ldc);

@@ -1,0 +1,289 @@
+// Y[M, N] = X[M, K] * W[N, K]^T for a batch of 9 to 64 rows on tcgen05: the decode-step product
+// when there are too many rows for the fragment-streaming kernel to stay bound by memory.
+//
+// The weights take the M side of the instruction: a CTA owns 128 rows of W and a slice of K, and
+// computes Y^T[128, batch] with UMMA M = 128, N = 16 / 32 / 64 (the batch rounded up; TMA fills
+// the missing rows of X with zeros).  Per K step of 64 a stage holds 16 KB of W from HBM and at
+// most 8 KB of X from L2, four stages deep, two CTAs to an SM, so every SM keeps tens of KB of
+// weights in flight.  K is cut into slices so that about two CTAs per SM exist even for narrow
+// outputs.  The CTAs that share a tile (1, 2, 4 or 8 slices of K) form a thread-block cluster:
+// each leaves its partial tile in its own shared memory, and after a cluster barrier each CTA adds
+// the slices, in slice order, for its share of the tile's rows, reading the other CTAs' shared
+// memory directly (distributed shared memory).  No scratch in global memory, and the sum does not
+// depend on timing.  With the gate/up rows of a SwiGLU interleaved in blocks of eight the
+// activation is applied in the same epilogue.
+//
+// Roles by warp as in the tiled kernel: warp 0 loads by TMA, warp 1 issues tcgen05.mma, warps
+// 2-5 read tensor memory (lane = weight row, column = batch row) and store.  Barrier waits are
+// bounded; a wait that gives up is recorded and read with gb_gemm_tc5_decode_status().
+#include "tc5.cuh"
+
+namespace {
+
+__device__ int g_status;
+
+constexpr int BMW = 128, BK = 64, STAGES = 4, THREADS = 192;
+constexpr int W_BYTES = BMW * BK * 2;
+
+__device__ __forceinline__ float silu_f(float x) {
+    if (x >= 0.f) return x / (1.f + expf(-x));
+    float e = expf(x);
+    return x * e / (1.f + e);
+}
+
+// value v of (weight row n, batch row b) -> Y, plain or through the SwiGLU epilogue; `other` is the
+// value of weight row n + 8 (the up row of a gate row), fetched by the caller with a shuffle
+template <typename TC>
+__device__ __forceinline__ void store_out(TC* __restrict__ Y, int64_t ldy, int b, int n, int N, float v, float other, int epi) {
+    if (epi == 0) {
+        if (n < N) Y[(int64_t)b * ldy + n] = from_f32<TC>(v);
+    } else {
+        if ((n & 15) < 8 && n + 8 < N) Y[(int64_t)b * ldy + ((n >> 4) << 3) + (n & 7)] = from_f32<TC>(silu_f(v) * other);
+    }
+}
+
+template <typename TC, int NB>  // NB = batch columns of the instruction: 16, 32 or 64
+__global__ void __launch_bounds__(THREADS) gemm_tc5_decode_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                 const __grid_constant__ CUtensorMap map_x, TC* __restrict__ Y,
+                                                                 int M, int N, int K, int64_t ldy, int splits, int kb_per_split,
+                                                                 int epi) {
+    constexpr int X_BYTES = NB * BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr int TMEM_COLS = NB < 32 ? 32 : NB;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BMW, split = blockIdx.y;
+    const int KB = (K + BK - 1) / BK;
+    const int kb0 = split * kb_per_split;
+    const int kb1 = kb0 + kb_per_split < KB ? kb0 + kb_per_split : KB;
+    const int KT = kb1 > kb0 ? kb1 - kb0 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < KT; kt++) {
+                const int s = kt % STAGES;
+                const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+                    atomicCAS(&g_status, 0, 1);
+                    abort_s = 1;
+                    break;
+                }
+                if (*(volatile int*)&abort_s) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                tma_load_2d(st, &map_w, (kb0 + kt) * BK, n0, &full_bar[s]);
+                tma_load_2d(st + W_BYTES, &map_x, (kb0 + kt) * BK, 0, &full_bar[s]);
+                issued = kt + 1;
+            }
+            if (*(volatile int*)&abort_s) {
+                for (int kt = issued > STAGES ? issued - STAGES : 0; kt < issued; kt++)
+                    mbar_wait(&full_bar[kt % STAGES], (uint32_t)(kt / STAGES) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(BMW, NB);
+            bool ok = true;
+            for (int kt = 0; kt < KT; kt++) {
+                const int s = kt % STAGES;
+                const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
+                if (!mbar_wait(&full_bar[s], phase)) {
+                    atomicCAS(&g_status, 0, 2);
+                    abort_s = 1;
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t w_addr = s32(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t adesc = smem_desc(w_addr), bdesc = smem_desc(w_addr + W_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)
+                    umma(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);
+            }
+            if (ok) umma_commit(&accum_bar);
+        }
+    } else {
+        const int quad = warp & 3;
+        const int n = n0 + quad * 32 + lane;  // this thread's weight row
+        bool have = KT > 0;
+        if (have && !mbar_wait(&accum_bar, 0)) {
+            atomicCAS(&g_status, 0, 3);
+            have = false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+        for (int c0 = 0; c0 < NB; c0 += 16) {
+            if (c0 >= M) break;
+            uint32_t r[16];
+            if (have) {
+                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) r[i] = 0u;
+            }
+            if (splits == 1) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    float v = __uint_as_float(r[i]);
+                    float other = __shfl_down_sync(0xffffffffu, v, 8);
+                    if (c0 + i < M) store_out<TC>(Y, ldy, c0 + i, n, N, v, other, epi);
+                }
+            } else {
+                // partial tile in this CTA's shared memory: part[b][row of the tile]; the operand
+                // stages are free, every product that read them has completed
+                float* part = reinterpret_cast<float*>(tiles);
+#pragma unroll
+                for (int i = 0; i < 16; i++) part[(c0 + i) * BMW + quad * 32 + lane] = __uint_as_float(r[i]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (splits == 1) return;
+
+    // all slices of the tile have left their partial tiles: add them, each CTA for its rows
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    {
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+        const int R = BMW / splits;  // rows of the tile this CTA adds up (16, 32 or 64)
+        const uint32_t part_addr = s32(tiles);
+        const int groups = (M * R + 31) / 32;
+        for (int it = warp; it < groups; it += THREADS / 32) {
+            const int idx = it * 32 + lane;
+            const int b = idx / R, nl = (int)rank * R + idx % R;
+            float v = 0.f;
+            if (b < M) {
+                for (int sl = 0; sl < splits; sl++) {
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(part_addr + (uint32_t)((b * BMW + nl) * 4)), "r"(sl));
+                    float x;
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(x) : "r"(remote) : "memory");
+                    v += x;
+                }
+            }
+            float other = __shfl_down_sync(0xffffffffu, v, 8);
+            if (b < M) store_out<TC>(Y, ldy, b, n0 + nl, N, v, other, epi);
+        }
+    }
+    // no CTA may leave while another still reads its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+constexpr int MAX_TILES = 8192;
+
+template <typename TC, int NB>
+int launch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldy, int epi, int splits,
+           cudaStream_t stream) {
+    constexpr int X_BYTES = NB * BK * 2;
+    int smem = STAGES * (W_BYTES + X_BYTES) + 1024;
+    const int part = NB * BMW * 4 + 1024;
+    if (part > smem) smem = part;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_decode_kernel<TC, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) GB_REFUSE("gemm_tc5_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_w, map_x;
+    if (int rc = tc5_make_map(&map_w, W, N, K, K, BMW)) return rc;
+    if (int rc = tc5_make_map(&map_x, X, M, K, ldx, NB)) return rc;
+    const int tiles = ceil_div(N, BMW);
+    const int KB = ceil_div(K, BK);
+    while (splits > 1 && KB < splits) splits >>= 1;
+    const int kb_per_split = ceil_div(KB, splits);
+    if (tiles > MAX_TILES) GB_REFUSE("gemm_tc5_decode: N = %d exceeds %d tiles", N, MAX_TILES);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc5_decode_kernel<TC, NB>, map_w, map_x, (TC*)Y, M, N, K, ldy, splits, kb_per_split, epi);
+    if (e != cudaSuccess) GB_REFUSE("gemm_tc5_decode: launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+template <typename TC>
+int dispatch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldy, int epi, int splits,
+             cudaStream_t stream) {
+    if (M <= 16) return launch<TC, 16>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    if (M <= 32) return launch<TC, 32>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    return launch<TC, 64>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+}
+
+}  // namespace
+
+// How many slices of K the kernel would like for this shape on a device with `sms` SMs (two CTAs
+// fit an SM): a power of two that keeps at most about 2 * sms CTAs, at least eight K steps of 64 a
+// slice, at most 8.
+GB_API int gb_gemm_tc5_decode_splits(int N, int K, int sms) {
+    int tiles = ceil_div(N, BMW), KB = ceil_div(K, BK);
+    int want = (2 * sms) / (tiles > 0 ? tiles : 1);
+    if (want > KB / 8) want = KB / 8;
+    int s = 1;
+    while (s * 2 <= want && s < 8) s *= 2;  // a cluster of 1, 2, 4 or 8 CTAs
+    return s;
+}
+
+// epi = 0: Y[M, N].  epi = 1: Y[M, N / 2] = silu(gate) * up with gate/up rows of W interleaved in
+// blocks of eight.  splits: 1, 2, 4 or 8 slices of K (the size of the cluster).
+GB_API int gb_gemm_tc5_decode(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
+                              int epi, int splits, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64) GB_REFUSE("gemm_tc5_decode: %d rows; this kernel takes at most 64", M);
+    if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5_decode: K = %d must be a positive multiple of 8", K);
+    if ((ldx & 7) || ldx < K) GB_REFUSE("gemm_tc5_decode: row stride %lld of X must be a multiple of 8 and at least K", (long long)ldx);
+    if (epi == 0 && ldy < N) GB_REFUSE("gemm_tc5_decode: row stride %lld of Y is shorter than N = %d", (long long)ldy, N);
+    if (epi == 1 && ((N & 15) || ldy < N / 2)) GB_REFUSE("gemm_tc5_decode: the SwiGLU epilogue needs N = %d to be a multiple of 16", N);
+    if (epi != 0 && epi != 1) GB_REFUSE("gemm_tc5_decode: unknown epilogue %d", epi);
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5_decode: operands must be 16-byte aligned");
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) GB_REFUSE("gemm_tc5_decode: %d slices; 1, 2, 4 or 8", splits);
+    if (c_dtype == GB_F32) return dispatch<float>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    if (c_dtype == GB_BF16) return dispatch<__nv_bfloat16>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    GB_REFUSE("gemm_tc5_decode: unknown output dtype %d", c_dtype);
+}
+
+GB_API int gb_gemm_tc5_decode_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return v;
+}

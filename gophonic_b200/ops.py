@@ -115,14 +115,40 @@ def add_rows(h: torch.Tensor, delta: torch.Tensor) -> None:
 
 
 # ---- feed-forward activation -------------------------------------------------------------
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r, i] = silu(gate_up[r, i]) * gate_up[r, I + i]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) -> None:
+    """out[r, i] = silu(gate[r, i]) * up[r, i]; gate and up are the two halves of ``gate_up``'s
+    columns, or, with ``interleave8``, alternate in blocks of eight columns."""
     _need(gate_up, "gate_up", dim=2)
     _need(out, "swiglu out", gate_up.dtype, 2)
     rows, two_i = gate_up.shape
     if two_i % 2 or out.shape != (rows, two_i // 2):
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
-    _check(_lib.gb_swiglu(_ptr(gate_up), _ptr(out), _code(out.dtype), c_int(rows), c_int(two_i // 2), _stream()))
+    _check(_lib.gb_swiglu(_ptr(gate_up), _ptr(out), _code(out.dtype), c_int(rows), c_int(two_i // 2),
+                          c_int(1 if interleave8 else 0), _stream()))
+
+
+def gemm_swiglu_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_swiglu`` takes this product: few rows, bfloat16, interleaved gate/up rows."""
+    return (_has("gb_gemm_skinny_swiglu") and a.shape[0] <= 64 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and w.shape[0] % 16 == 0 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto") -> None:
+    """out[M, N/2] = silu(a Wg^T) * (a Wu^T) in one kernel, for at most 64 rows; ``w`` [N, K] holds
+    gate and up rows interleaved in blocks of eight."""
+    _need(a, "gemm a", torch.bfloat16, 2, contiguous=False)
+    _need(w, "gemm w", torch.bfloat16, 2)
+    _need(out, "gemm out", dim=2, contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N // 2) or out.stride(1) != 1 or not gemm_swiglu_accepts(a, w):
+        raise KernelError(f"gemm_swiglu: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if M > SKINNY_MAX_ROWS and algo != "skinny" and _has("gb_gemm_tc5_decode") or algo == "tc5_decode":
+        _tc5_decode(a, w, out, 1)
+        return
+    _check(_lib.gb_gemm_skinny_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                      c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
 
 
 # ---- matrix products ---------------------------------------------------------------------
@@ -170,7 +196,11 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
         gemm_simt(a, w, out)
         return "simt"
     if algo == "auto":
-        if M <= 64 and _has("gb_gemm_skinny"):
+        if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT and _has("gb_gemm_skinny"):
+            algo = "skinny"
+        elif M <= 64 and _has("gb_gemm_tc5_decode"):
+            algo = "tc5_decode"
+        elif M <= 64 and _has("gb_gemm_skinny"):
             algo = "skinny"
         elif _has("gb_gemm_tc5") and M >= 128 and tc5_accepts(a, w, out):
             algo = "tc5"
@@ -187,11 +217,34 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     elif algo == "tc5":
         _check(_lib.gb_gemm_tc5(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                 c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    elif algo == "tc5_decode":
+        _tc5_decode(a, w, out, 0)
     elif algo == "simt":
         gemm_simt(a, w, out)
     else:
         raise KernelError(f"gemm: unknown algorithm '{algo}'")
     return algo
+
+
+# rows up to which the fragment-streaming kernel is used for decode; above it (to 64) the tcgen05
+# split-K kernel takes over
+SKINNY_MAX_ROWS = 8
+# outputs this wide (the head) have enough tiles to fill the GPU without cutting K; the tcgen05
+# kernel then streams them a little faster than the fragment kernel at every row count
+WIDE_OUTPUT = 32768
+
+_sm_count = {}
+
+
+def _tc5_decode(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> None:
+    M, K = a.shape
+    N = w.shape[0]
+    dev = a.device
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(N), c_int(K), c_int(_sm_count[dev])))
+    _check(_lib.gb_gemm_tc5_decode(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                   c_int64(a.stride(0)), c_int64(out.stride(0)), c_int(epi), c_int(splits), _stream()))
 
 
 def tc5_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -202,9 +255,11 @@ def tc5_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 def tc5_status() -> int:
     """0, or which role of a tcgen05 kernel gave up waiting on a barrier since the last call."""
-    if not _has("gb_gemm_tc5_status"):
-        return 0
-    return int(_lib.gb_gemm_tc5_status())
+    code = 0
+    for name in ("gb_gemm_tc5_status", "gb_gemm_tc5_decode_status"):
+        if _has(name):
+            code = code or int(getattr(_lib, name)())
+    return code
 
 
 # ---- attention ---------------------------------------------------------------------------

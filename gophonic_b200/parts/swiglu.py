@@ -25,7 +25,16 @@ class SwiGLU(FeedForward):
         gate, up = tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]
         if gate.dtype != up.dtype:
             raise ValueError(f"{prefix}: gate_proj is {gate.dtype} and up_proj is {up.dtype}; they must agree")
-        self.gate_up = torch.cat([gate, up], dim=0).contiguous()
+        # bfloat16 weights whose width allows it are kept with gate and up rows alternating in blocks
+        # of eight, so the few-row kernel can apply the activation in its epilogue
+        # (internal/qwen3lm/gpu_darwin.go:406-417 interleaves gate/up rows for the same reason)
+        inter, hidden = spec.intermediate, spec.hidden
+        self.interleaved = gate.dtype == torch.bfloat16 and inter % 8 == 0
+        if self.interleaved:
+            self.gate_up = torch.stack([gate.view(inter // 8, 8, hidden), up.view(inter // 8, 8, hidden)], dim=1) \
+                .reshape(2 * inter, hidden).contiguous()
+        else:
+            self.gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.down = tensors[prefix + "down_proj.weight"].contiguous()
 
     def weight_bytes(self) -> int:
@@ -34,8 +43,11 @@ class SwiGLU(FeedForward):
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
         ops = self.rt.ops
         rows = x.shape[0]
-        gu = torch.empty((rows, 2 * self.spec.intermediate), dtype=x.dtype, device=x.device)
-        ops.gemm(x, self.gate_up, gu)
         act = torch.empty((rows, self.spec.intermediate), dtype=x.dtype, device=x.device)
-        ops.swiglu(gu, act)
+        if self.interleaved and ops.gemm_swiglu_accepts(x, self.gate_up):
+            ops.gemm_swiglu(x, self.gate_up, act)
+        else:
+            gu = torch.empty((rows, 2 * self.spec.intermediate), dtype=x.dtype, device=x.device)
+            ops.gemm(x, self.gate_up, gu)
+            ops.swiglu(gu, act, self.interleaved)
         ops.gemm(act, self.down, out)

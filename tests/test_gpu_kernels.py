@@ -89,6 +89,30 @@ def test_swiglu(ops, dtype, inter):
     assert torch.isfinite(o).all() and o[0, 1] == 100.0 and abs(o[0, 0].item()) < 1e-30
 
 
+@pytest.mark.parametrize("M", [1, 8, 9, 33, 64])
+@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (1000, 96), (12288 // 8, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
+    """gate/up rows interleaved in blocks of eight; the few-row kernel applies silu(gate) * up itself,
+    and the stand-alone kernel reads the same interleaved layout."""
+    gate, up = rnd(inter, K, dtype=torch.bfloat16, scale=0.2, seed=1), rnd(inter, K, dtype=torch.bfloat16, scale=0.2, seed=2)
+    w = torch.stack([gate.view(inter // 8, 8, K), up.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
+    x = rnd(M, K, dtype=torch.bfloat16, seed=3)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    ref = g / (1 + torch.exp(-g)) * u
+    assert ops.gemm_swiglu_accepts(x, w)
+    for algo in ("skinny", "tc5_decode"):
+        out = torch.full((M, inter), float("nan"), dtype=out_dtype, device=DEV)
+        ops.gemm_swiglu(x, w, out, algo=algo)
+        close(out, ref, 2e-5 if out_dtype == torch.float32 else 6e-3)
+    assert ops.tc5_status() == 0
+    gu = torch.empty((M, 2 * inter), dtype=torch.bfloat16, device=DEV)
+    ops.gemm(x, w, gu)
+    out2 = torch.empty((M, inter), dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gu, out2, True)
+    close(out2, ref, 1.2e-2)
+
+
 # ---- matrix products ----------------------------------------------------------------------
 SHAPES = [(1, 64, 64), (3, 1000, 96), (17, 136, 80), (64, 333, 160), (65, 192, 96), (130, 520, 264), (257, 96, 4104)]
 
@@ -112,7 +136,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
     assert torch.equal(one[0], full[67])
 
 
-@pytest.mark.parametrize("algo", ["skinny", "mma", "tc5"])
+@pytest.mark.parametrize("algo", ["skinny", "mma", "tc5", "tc5_decode"])
 @pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (300, 1000, 512), (2048, 512, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
@@ -120,7 +144,7 @@ def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
         pytest.skip(f"kernel {algo} is not built")
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
     out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    if algo == "skinny" and M > 64:
+    if algo in ("skinny", "tc5_decode") and M > 64:
         with pytest.raises(ops.KernelError):
             ops.gemm(a, w, out, algo=algo)
         return
@@ -129,7 +153,7 @@ def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
             ops.gemm(a, w, out, algo=algo)
         return
     ops.gemm(a, w, out, algo=algo)
-    if algo == "tc5":
+    if algo.startswith("tc5"):
         assert ops.tc5_status() == 0, "a tcgen05 kernel gave up waiting on a barrier"
     close(out, a.double() @ w.double().T, 2e-5 if out_dtype == torch.float32 else 6e-3)
 
