@@ -227,11 +227,36 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     out[(int64_t)r * inter + i] = from_f32<T>(silu_f32(a) * b);
 }
 
+// bfloat16, width a multiple of 8: eight outputs a thread, 16-byte loads and stores
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
+                                     int interleave8) {
+    const int r = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= inter) return;
+    const __nv_bfloat16* g = gu + (int64_t)r * 2 * inter;
+    const int gi = interleave8 ? i * 2 : i, ui = interleave8 ? i * 2 + 8 : inter + i;
+    const uint4 a = *reinterpret_cast<const uint4*>(g + gi), b = *reinterpret_cast<const uint4*>(g + ui);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        o2[j] = __floats2bfloat162_rn(silu_f32(__low2float(a2[j])) * __low2float(b2[j]), silu_f32(__high2float(a2[j])) * __high2float(b2[j]));
+    *reinterpret_cast<uint4*>(out + (int64_t)r * inter + i) = o;
+}
+
 GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, int interleave8, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (inter <= 0) GB_REFUSE("swiglu: width %d", inter);
     if (interleave8 && (inter & 7)) GB_REFUSE("swiglu: interleaved columns need a width that is a multiple of 8, got %d", inter);
     if (rows > 65535) GB_REFUSE("swiglu: %d rows exceed one launch (65535); the step splits larger batches", rows);
+    if (dtype == GB_BF16 && (inter & 7) == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
+        swiglu_bf16x8_kernel<<<dim3(ceil_div(inter / 8, 128), rows), 128, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter,
+                                                                                     interleave8);
+        GB_CHECK_LAUNCH("swiglu");
+        return 0;
+    }
     dim3 grid(ceil_div(inter, 256), rows);
     if (dtype == GB_F32)
         swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, 2 * (int64_t)inter, interleave8);
@@ -337,6 +362,62 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     }
 }
 
+// The common geometry (bfloat16, head_dim 128 rotated in full): a warp per (row, head), every lane
+// holds four consecutive elements, so element i and its partner i + 64 sit in lanes l and l ^ 16.
+__global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x;
+    const int head = blockIdx.y * 8 + warp;
+    const int total_heads = p.heads + 2 * p.kv_heads;
+    if (head >= total_heads) return;
+    typedef __nv_bfloat16 bf;
+    bf* src = (bf*)p.qkv + (int64_t)r * p.row_stride + (int64_t)head * 128 + lane * 4;
+    const int pos = p.row_pos[r];
+    const bool is_q = head < p.heads;
+    const bool is_k = !is_q && head < p.heads + p.kv_heads;
+    bf* dst = src;
+    if (!is_q) {
+        if (!p.write_kv) return;
+        const int kvh = is_k ? head - p.heads : head - p.heads - p.kv_heads;
+        const int slot = p.seq_slot[p.row_seq[r]];
+        const int64_t page = page_of(p.block_table + (int64_t)slot * p.bt_stride, pos, p.ring_pages);
+        bf* plane = (bf*)(is_k ? p.k_plane : p.v_plane);
+        dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)128 + lane * 4;
+    }
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    if (!is_q && !is_k) {
+        *reinterpret_cast<uint2*>(dst) = raw;
+        return;
+    }
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    float y[4] = {__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi)};
+    const float* w = is_q ? p.q_w : p.k_w;
+    if (w) {
+        float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+        const float inv = 1.0f / sqrtf(ss / 128.f + p.eps);
+        const float4 ww = *reinterpret_cast<const float4*>(w + lane * 4);
+        y[0] = y[0] * inv * ww.x;
+        y[1] = y[1] * inv * ww.y;
+        y[2] = y[2] * inv * ww.z;
+        y[3] = y[3] * inv * ww.w;
+    }
+    const int ci = (lane & 15) * 4;  // index into the 64 angles of this position
+    const float4 c = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)pos * 64 + ci);
+    const float4 s = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)pos * 64 + ci);
+    const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float partner = __shfl_xor_sync(0xffffffffu, y[j], 16);
+        o[j] = lane < 16 ? y[j] * cs[j] - partner * sn[j] : y[j] * cs[j] + partner * sn[j];
+    }
+    const __nv_bfloat162 o0 = __floats2bfloat162_rn(o[0], o[1]), o1 = __floats2bfloat162_rn(o[2], o[3]);
+    uint2 out;
+    out.x = *reinterpret_cast<const uint32_t*>(&o0);
+    out.y = *reinterpret_cast<const uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(dst) = out;
+}
+
 GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStream_t stream) {
     QkRopeParams p = *pp;
     if (p.rows <= 0) return 0;
@@ -346,6 +427,13 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     if (p.heads <= 0 || p.kv_heads < 0) GB_REFUSE("qk_norm_rope: heads %d, kv heads %d", p.heads, p.kv_heads);
     if (p.rows > 0x7fffffff / 2) GB_REFUSE("qk_norm_rope: %d rows are too many", p.rows);
     int total_heads = p.heads + 2 * p.kv_heads;
+    if (dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
+        !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
+        ceil_div(total_heads, 8) <= 65535) {
+        qk_rope_bf16_d128_kernel<<<dim3(p.rows, ceil_div(total_heads, 8)), 256, 0, stream>>>(p);
+        GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
+        return 0;
+    }
     dim3 grid(p.rows, ceil_div(total_heads, 4));
     if (grid.y > 65535) GB_REFUSE("qk_norm_rope: %d heads exceed one launch", total_heads);
     size_t smem = (size_t)4 * p.d * sizeof(float);

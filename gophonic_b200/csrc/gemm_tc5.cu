@@ -1,15 +1,17 @@
 // C[M, N] = A[M, K] * W[N, K]^T, bfloat16 operands, on the fifth-generation tensor cores:
 // tcgen05.mma with the accumulator in tensor memory, operands brought into shared memory by TMA.
 //
-// One CTA computes a 128 x 256 tile.  Roles, by warp:
+// Tiles are 128 x 256; one CTA per SM walks them (M tile fastest).  Tensor memory holds two
+// accumulators, so the epilogue of a tile runs while the products of the next tile are issued.
+// Roles, by warp:
 //   warp 0   one lane issues the TMA loads (cp.async.bulk.tensor.2d) of a 128 x 64 slab of A and a
 //            256 x 64 slab of W per stage into 128-byte-swizzled shared memory, four stages deep;
-//   warp 1   allocates 256 columns of tensor memory; one lane issues four tcgen05.mma
-//            (M 128, N 256, K 16) per stage and commits the stage's barrier when they are done;
-//   warps 2-5  wait for the last commit, read the accumulator with tcgen05.ld (each warp the 32
-//            lanes of its quadrant), convert and store 32 columns at a time.
-// CTAs are numbered with the M tile fastest, so the CTAs that run together share their W slabs
-// and W crosses HBM once.  Edges: TMA fills rows and columns outside the operands with zeros and
+//   warp 1   allocates all 512 columns of tensor memory; one lane issues four tcgen05.mma
+//            (M 128, N 256, K 16) per stage and commits the stage's barrier when they are done,
+//            and the accumulator's barrier after a tile's last step;
+//   warps 2-5  wait for an accumulator, read it with tcgen05.ld (each warp the 32 lanes of its
+//            quadrant), convert and store 32 columns at a time, then hand the accumulator back.
+// Tiles that run together share their W slabs, so W crosses HBM once.  Edges: TMA fills rows and columns outside the operands with zeros and
 // the stores are bounded, so M, N and K need no padding (K and the row strides must be multiples
 // of 8 elements, the 16-byte rule of TMA).
 //
@@ -24,31 +26,39 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 256;
+constexpr int TMEM_COLS = 512;  // two accumulators of 256 columns
 constexpr int THREADS = 192;
 
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
+}
 
 template <typename TC>
 __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, TC* __restrict__ C, int M, int N,
-                                                          int K, int64_t ldc) {
+                                                          int K, int64_t ldc, int epi) {
     extern __shared__ unsigned char smem_raw[];
     // operand stages need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int KT = (K + BK - 1) / BK;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int total = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&accum_bar, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+        }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -62,99 +72,169 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
 
+    // A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tiles are numbered with the M tile
+    // fastest, so CTAs that run together share their W slabs.
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kt = 0; kt < KT; kt++) {
-                const int s = kt % STAGES;
-                const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
-                if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
-                    atomicCAS(&g_tc5_status, 0, 1);
-                    abort_s = 1;
-                    break;
+            int it = 0;  // K steps issued so far, over all tiles
+            bool stop = false;
+            for (int tile = blockIdx.x; tile < total && !stop; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                for (int kt = 0; kt < KT; kt++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+                        atomicCAS(&g_tc5_status, 0, 1);
+                        abort_s = 1;
+                    }
+                    if (*(volatile int*)&abort_s) {
+                        stop = true;
+                        break;
+                    }
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                    tma_load_2d(st, &map_a, kt * BK, m0, &full_bar[s]);
+                    tma_load_2d(st + A_BYTES, &map_w, kt * BK, n0, &full_bar[s]);
                 }
-                if (*(volatile int*)&abort_s) break;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-                tma_load_2d(st, &map_a, kt * BK, m0, &full_bar[s]);
-                tma_load_2d(st + A_BYTES, &map_w, kt * BK, n0, &full_bar[s]);
-                issued = kt + 1;
             }
-            if (*(volatile int*)&abort_s) {
+            if (stop) {
                 // let the copies that are still in flight land before the CTA leaves
-                for (int kt = issued > STAGES ? issued - STAGES : 0; kt < issued; kt++)
-                    mbar_wait(&full_bar[kt % STAGES], (uint32_t)(kt / STAGES) & 1u);
+                for (int j = it > STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&full_bar[j % STAGES], (uint32_t)(j / STAGES) & 1u);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, BN);
-            bool ok = true;
-            for (int kt = 0; kt < KT; kt++) {
-                const int s = kt % STAGES;
-                const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
-                if (!mbar_wait(&full_bar[s], phase)) {
-                    atomicCAS(&g_tc5_status, 0, 2);
+            int it = 0, i = 0;
+            bool stop = false;
+            for (int tile = blockIdx.x; tile < total && !stop; tile += gridDim.x, i++) {
+                const int buf = i & 1;
+                const uint32_t use = (uint32_t)(i >> 1) & 1u;
+                // the epilogue must have drained this accumulator (passes at once on its first use)
+                if (!mbar_wait(&acc_empty[buf], use ^ 1u)) {
+                    atomicCAS(&g_tc5_status, 0, 4);
                     abort_s = 1;
-                    ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t a_addr = s32(tiles + (size_t)s * STAGE_BYTES);
-                const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kt = 0; kt < KT; kt++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&full_bar[s], phase)) {
+                        atomicCAS(&g_tc5_status, 0, 2);
+                        abort_s = 1;
+                        stop = true;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t a_addr = s32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++) {
-                    // 16 elements of K = 32 bytes = 2 units of the descriptor's address field
-                    umma(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; k++) {
+                        // 16 elements of K = 32 bytes = 2 units of the descriptor's address field
+                        umma(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);  // the stage is free once these products have read it
                 }
-                umma_commit(&empty_bar[s]);  // the stage is free once these products have read it
+                if (!stop) umma_commit(&acc_full[buf]);
             }
-            if (ok) umma_commit(&accum_bar);
         }
     } else {
-        // epilogue: warp w reads the tensor-memory lanes of quadrant w % 4
+        // epilogue: warp w reads the tensor-memory lanes of quadrant w % 4, while the next tile's
+        // products already run into the other accumulator
         const int quad = warp & 3;
-        const int row = m0 + quad * 32 + lane;
-        if (mbar_wait(&accum_bar, 0)) {
+        const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0);
+        int i = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, i++) {
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            const int buf = i & 1;
+            const uint32_t use = (uint32_t)(i >> 1) & 1u;
+            const int row = m0 + quad * 32 + lane;
+            if (!mbar_wait(&acc_full[buf], use)) {
+                atomicCAS(&g_tc5_status, 0, 3);
+                break;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= N) break;  // uniform across the warp
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld32(t_addr + (uint32_t)c0, r);
+                if (epi == 1) {
+                    // columns alternate in blocks of eight between gate and up outputs of a SwiGLU:
+                    // sixteen activations per 32 columns, out[row, (n0 + c0) / 2 + ...]
+                    if (row < M) {
+                        float act[16];
+#pragma unroll
+                        for (int j = 0; j < 2; j++)
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                float g = __uint_as_float(r[16 * j + e]), u = __uint_as_float(r[16 * j + 8 + e]);
+                                // g / (1 + e^-g): for very negative g the exponential overflows to +inf and
+                                // the quotient is -0, the limit of the function
+                                act[8 * j + e] = __fdividef(g, 1.f + __expf(-g)) * u;
+                            }
+                        TC* dst = C + (int64_t)row * ldc + ((n0 + c0) >> 1);
+                        const int left = (N - (n0 + c0)) >> 1;  // outputs that exist from here on
+                        if (vec_ok && left >= 16 && sizeof(TC) == 2) {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                uint4 v;
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(act[e * 8 + 0], act[e * 8 + 1]);
+                                __nv_bfloat162 t1 = __floats2bfloat162_rn(act[e * 8 + 2], act[e * 8 + 3]);
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(act[e * 8 + 4], act[e * 8 + 5]);
+                                __nv_bfloat162 t3 = __floats2bfloat162_rn(act[e * 8 + 6], act[e * 8 + 7]);
+                                v.x = *reinterpret_cast<uint32_t*>(&t0);
+                                v.y = *reinterpret_cast<uint32_t*>(&t1);
+                                v.z = *reinterpret_cast<uint32_t*>(&t2);
+                                v.w = *reinterpret_cast<uint32_t*>(&t3);
+                                d4[e] = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 16; e++)
+                                if (e < left) dst[e] = from_f32<TC>(act[e]);
+                        }
+                    }
+                    continue;
+                }
                 if (row < M) {
                     TC* dst = C + (int64_t)row * ldc + n0 + c0;
                     if (vec_ok && n0 + c0 + 32 <= N) {
                         if (sizeof(TC) == 2) {
                             uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
+                            for (int e = 0; e < 4; e++) {
                                 uint4 v;
-                                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
-                                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
-                                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
-                                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[e * 8 + 0]), __uint_as_float(r[e * 8 + 1]));
+                                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[e * 8 + 2]), __uint_as_float(r[e * 8 + 3]));
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[e * 8 + 4]), __uint_as_float(r[e * 8 + 5]));
+                                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[e * 8 + 6]), __uint_as_float(r[e * 8 + 7]));
                                 v.x = *reinterpret_cast<uint32_t*>(&t0);
                                 v.y = *reinterpret_cast<uint32_t*>(&t1);
                                 v.z = *reinterpret_cast<uint32_t*>(&t2);
                                 v.w = *reinterpret_cast<uint32_t*>(&t3);
-                                d4[i] = v;
+                                d4[e] = v;
                             }
                         } else {
                             uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-                            for (int i = 0; i < 8; i++) d4[i] = make_uint4(r[i * 4], r[i * 4 + 1], r[i * 4 + 2], r[i * 4 + 3]);
+                            for (int e = 0; e < 8; e++) d4[e] = make_uint4(r[e * 4], r[e * 4 + 1], r[e * 4 + 2], r[e * 4 + 3]);
                         }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            if (n0 + c0 + i < N) dst[i] = from_f32<TC>(__uint_as_float(r[i]));
+                        for (int e = 0; e < 32; e++)
+                            if (n0 + c0 + e < N) dst[e] = from_f32<TC>(__uint_as_float(r[e]));
                     }
                 }
             }
-        } else {
-            atomicCAS(&g_tc5_status, 0, 3);
+            // this warp has read its part of the accumulator: hand the buffer back
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -166,7 +246,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant
 }
 
 template <typename TC>
-int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream) {
+int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, int epi, cudaStream_t stream) {
     const int smem = STAGES * STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -177,25 +257,44 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
     CUtensorMap map_a, map_w;
     if (int rc = tc5_make_map(&map_a, A, M, K, lda, BM)) return rc;
     if (int rc = tc5_make_map(&map_w, W, N, K, K, BN)) return rc;
-    dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
-    if (grid.y > 65535) GB_REFUSE("gemm_tc5: N = %d exceeds one launch", N);
-    gemm_tc5_kernel<TC><<<grid, THREADS, smem, stream>>>(map_a, map_w, (TC*)C, M, N, K, ldc);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int64_t total = (int64_t)ceil_div(M, BM) * ceil_div(N, BN);
+    if (total > 0x7fffffff) GB_REFUSE("gemm_tc5: %lld tiles are too many", (long long)total);
+    const int grid = total < sms ? (int)total : sms;  // one CTA per SM walks the tiles
+    gemm_tc5_kernel<TC><<<grid, THREADS, smem, stream>>>(map_a, map_w, (TC*)C, M, N, K, ldc, epi);
     GB_CHECK_LAUNCH("gemm_tc5");
     return 0;
 }
 
 }  // namespace
 
-GB_API int gb_gemm_tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
-                       cudaStream_t stream) {
+static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, int epi,
+               cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5: K = %d must be a positive multiple of 8", K);
     if ((lda & 7) || lda < K) GB_REFUSE("gemm_tc5: row stride %lld of A must be a multiple of 8 and at least K", (long long)lda);
-    if (ldc < N) GB_REFUSE("gemm_tc5: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
+    if (epi == 0 && ldc < N) GB_REFUSE("gemm_tc5: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
+    if (epi == 1 && ((N & 15) || ldc < N / 2)) GB_REFUSE("gemm_tc5: the SwiGLU epilogue needs N = %d to be a multiple of 16", N);
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5: operands must be 16-byte aligned");
-    if (c_dtype == GB_F32) return launch<float>(A, W, C, M, N, K, lda, ldc, stream);
-    if (c_dtype == GB_BF16) return launch<__nv_bfloat16>(A, W, C, M, N, K, lda, ldc, stream);
+    if (c_dtype == GB_F32) return launch<float>(A, W, C, M, N, K, lda, ldc, epi, stream);
+    if (c_dtype == GB_BF16) return launch<__nv_bfloat16>(A, W, C, M, N, K, lda, ldc, epi, stream);
     GB_REFUSE("gemm_tc5: unknown output dtype %d", c_dtype);
+}
+
+GB_API int gb_gemm_tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
+                       cudaStream_t stream) {
+    return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, 0, stream);
+}
+
+// C[M, N / 2] = silu(A Wg^T) * (A Wu^T); W holds gate and up rows interleaved in blocks of eight.
+GB_API int gb_gemm_tc5_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
+                              cudaStream_t stream) {
+    return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, 1, stream);
 }
 
 // 0 if no tcgen05 kernel has given up on a barrier since the last call; else the role that did

@@ -128,8 +128,10 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) 
 
 
 def gemm_swiglu_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether ``gemm_swiglu`` takes this product: few rows, bfloat16, interleaved gate/up rows."""
-    return (_has("gb_gemm_skinny_swiglu") and a.shape[0] <= 64 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    """Whether ``gemm_swiglu`` takes this product: bfloat16, interleaved gate/up rows, and a row
+    count one of the kernels with the fused epilogue handles (up to 64, or at least 128)."""
+    return (_has("gb_gemm_skinny_swiglu") and (a.shape[0] <= 64 or (a.shape[0] >= 128 and _has("gb_gemm_tc5_swiglu")))
+            and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and w.shape[0] % 16 == 0 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
 
@@ -144,6 +146,10 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2) or out.stride(1) != 1 or not gemm_swiglu_accepts(a, w):
         raise KernelError(f"gemm_swiglu: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if M > 64:
+        _check(_lib.gb_gemm_tc5_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                       c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+        return
     if M > SKINNY_MAX_ROWS and algo != "skinny" and _has("gb_gemm_tc5_decode") or algo == "tc5_decode":
         _tc5_decode(a, w, out, 1)
         return
