@@ -166,6 +166,82 @@ def time_prefill(engine, tokens, iters, warmup, torch):
     return statistics.median(times)
 
 
+def probe(name):
+    """Run one kernel of the step a few times on a small, fixed workload (operands larger than L2
+    where the kernel is bound by memory), for profilers.  Prints the kernel's own timing."""
+    import torch
+    from gophonic_b200 import ops
+    dev = "cuda:0"
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, device=dev, generator=g) * scale).to(bf)
+
+    if name in ("gemm_prefill", "gemm_prefill_swiglu"):
+        M, N, K = 2048, 24576, 4096       # gate/up of one layer: 201 MB of weights
+        a, w = rnd(M, K), rnd(N, K, scale=0.05)
+        out = torch.empty((M, N // 2 if name.endswith("swiglu") else N), dtype=bf, device=dev)
+        fn = (lambda: ops.gemm_swiglu(a, w, out)) if name.endswith("swiglu") else (lambda: ops.gemm(a, w, out, algo="tc5"))
+        work = 2.0 * M * N * K
+        unit = "TFLOP/s"
+    elif name in ("gemm_decode_b8", "gemm_decode_b64"):
+        M = 8 if name.endswith("b8") else 64
+        N, K = 24576, 4096
+        ws = [rnd(N, K, scale=0.05) for _ in range(3)]   # rotate 600 MB of weights through L2
+        a = rnd(M, K)
+        out = torch.empty((M, N), dtype=bf, device=dev)
+        state = {"i": 0}
+
+        def fn():
+            ops.gemm(a, ws[state["i"] % 3], out)
+            state["i"] += 1
+        work = N * K * 2.0
+        unit = "GB/s"
+    elif name in ("attn_decode_b8", "attn_decode_b64", "attn_prefill"):
+        heads, kvh, d = 32, 8, 128
+        if name == "attn_prefill":
+            nseq, q_len, kv_len = 1, 2048, 2048
+        else:
+            nseq, q_len, kv_len = (8 if name.endswith("b8") else 64), 1, 4096
+        pages_per = (kv_len + 63) // 64
+        n_pages = nseq * pages_per
+        k = rnd(n_pages, kvh, 64, d)
+        v = rnd(n_pages, kvh, 64, d)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(nseq, pages_per)
+        q = rnd(nseq * q_len, heads * d)
+        out = torch.empty_like(q)
+        ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        slot, start = ints(list(range(nseq))), ints([i * q_len for i in range(nseq)])
+        ql, kl = ints([q_len] * nseq), ints([kv_len] * nseq)
+        from gophonic_b200.engine.step import choose_splits
+        splits = 1 if q_len > 1 else choose_splits(nseq * kvh, kv_len)
+        scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, d, splits), dtype=torch.float32, device=dev) if splits > 1 else None
+
+        def fn():
+            ops.attention(q, out, k, v, table, 0, slot, start, ql, kl, nseq, q_len, heads, kvh, d, d ** -0.5, 0, splits, scratch)
+        if q_len == 1:
+            work, unit = 2.0 * n_pages * kvh * 64 * d * 2, "GB/s"
+        else:
+            work, unit = 2.0 * heads * d * q_len * q_len, "TFLOP/s"
+    else:
+        raise SystemExit(f"unknown probe '{name}'")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 3
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"probe": name, "ms": round(ms, 4), "rate": round(rate, 1), "unit": unit, "status": ops.tc5_status()}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -175,7 +251,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    ap.add_argument("--probe", default="", help="run one kernel on a small fixed workload (for profilers) and exit")
     args = ap.parse_args()
+    if args.probe:
+        return probe(args.probe)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "GetStream/gophonic is a Go module (no setup.py/pyproject; pip "
                           "refuses it), there is no Go toolchain here, and its GPU paths are Metal/WebGPU only"}))
