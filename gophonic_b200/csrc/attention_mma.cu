@@ -238,6 +238,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [16][SD]
     bf16* KV = Qs + 16 * SD;                          // [DSTAGES][2][64][SD]
 
+    pdl_trigger();  // the product that follows may start fetching its weights
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int G = p.heads / p.kv_heads;
     const int GC = G < 16 ? G : 16;

@@ -69,3 +69,27 @@ __device__ __forceinline__ int64_t page_of(const int* __restrict__ bt, int pos, 
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may begin while the kernel before it on the stream is still running; it must call pdl_wait()
+// before it touches anything that kernel writes (or writes anything that kernel reads).  A kernel
+// calls pdl_trigger() once the kernel after it may begin its independent prologue.  Both are
+// no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// Launch `kernel` so that it may overlap the tail of its predecessor (see pdl_wait).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

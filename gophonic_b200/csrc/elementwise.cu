@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_vec_kernel(float* __restr
                                                                   const int* __restrict__ row_index) {
     __shared__ float warp_part[THREADS / 32];
     __shared__ float inv_s;
+    pdl_trigger();  // the product that follows may start fetching its weights
     const int orow = blockIdx.x;
     const int row = row_index ? row_index[orow] : orow;
     float4* hr = reinterpret_cast<float4*>(h + (int64_t)row * n);

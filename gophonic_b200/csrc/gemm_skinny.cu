@@ -11,6 +11,8 @@
 // fixed order through shared memory, so results do not depend on the batch around a row.
 #include "mma.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
 int g_max_kw = 0;      // most warps that split K inside a CTA (0: chosen by shape)
@@ -47,7 +49,34 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
     if (k_end > K) k_end = K;
     const int k_full = k_begin + ((k_end - k_begin) / 32) * 32;
 
+    // The weights do not depend on the kernel before this one: start this warp's first weight
+    // loads while that kernel may still be running (programmatic dependent launch), then wait for
+    // it, let the kernel after this one start its own prologue, and only then read activations.
     int k = k_begin;
+    constexpr int PRE = 4;
+    if (k + PRE * 32 <= k_full) {
+        uint4 a_lo[PRE], a_hi[PRE];
+#pragma unroll
+        for (int u = 0; u < PRE; u++) {
+            a_lo[u] = ld_stream16(w_lo + k + u * 32);
+            a_hi[u] = ld_stream16(w_hi + k + u * 32);
+        }
+        pdl_wait();
+        pdl_trigger();
+#pragma unroll
+        for (int u = 0; u < PRE; u++) {
+#pragma unroll
+            for (int j = 0; j < MT; j++) {
+                uint4 xb = *reinterpret_cast<const uint4*>(xp[j] + k + u * 32);
+                mma_bf16_16816(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, xb.x, xb.y);
+                mma_bf16_16816(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, xb.z, xb.w);
+            }
+        }
+        k += PRE * 32;
+    } else {
+        pdl_wait();
+        pdl_trigger();
+    }
 #pragma unroll 4
     for (; k < k_full; k += 32) {
         uint4 a_lo = ld_stream16(w_lo + k);
@@ -127,6 +156,17 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
     while (kw < max_kw && steps / (kw * 2) >= g_min_steps) kw *= 2;
     int k_per_warp = ceil_div(steps, kw) * 32;
     size_t smem = (size_t)kw * 16 * MT * 8 * sizeof(float);
+    static int mode = -1;  // experiment switch: bit 0 programmatic launch
+    if (mode < 0) {
+        const char* m = getenv("GB_SKINNY_MODE");
+        mode = m ? atoi(m) : 1;
+    }
+    if (mode & 1) {
+        cudaError_t e = launch_pdl(gemm_skinny_kernel<MT>, dim3(ceil_div(N, 16)), dim3(kw * 32), smem, stream, (const __nv_bfloat16*)X,
+                                   (const __nv_bfloat16*)W, Y, (int)(c_dtype == GB_BF16), M, N, K, ldx, ldy, k_per_warp, epi);
+        if (e != cudaSuccess) GB_REFUSE("gemm_skinny: launch failed: %s", cudaGetErrorString(e));
+        return 0;
+    }
     gemm_skinny_kernel<MT><<<ceil_div(N, 16), kw * 32, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, Y,
                                                                       c_dtype == GB_BF16, M, N, K, ldx, ldy, k_per_warp, epi);
     GB_CHECK_LAUNCH("gemm_skinny");
