@@ -1,0 +1,481 @@
+// Flash attention for prompts on the fifth-generation tensor cores (bfloat16, head_dim 128).
+//
+// A CTA owns 256 query rows of one head of one sequence, as two groups of 128, and walks the
+// sequence's keys one cache page (64 keys) at a time.  Both products of a step run as tcgen05.mma
+// with the accumulators in tensor memory:
+//     S_g = Q_g K^T   (M 128, N 64 keys, K 128)   -> two S buffers of 64 columns per group
+//     O_g += P_g V    (M 128, N 128, K 64 keys)    -> one O buffer of 128 columns per group
+// Roles by warp: warp 0 loads by TMA (the query tiles once; per page two boxes of keys and two of
+// values straight from the paged cache, three stages deep); one thread of warp 1 and one of warp 2
+// issue the products of group A and B; warps 3-6 and 7-10 are the softmax of group A and B: each
+// thread owns one query row, reads its row of S
+// from tensor memory, keeps the running maximum and sum, and writes the probabilities as bfloat16
+// into shared memory in the operand layout of the second product.  O stays in tensor memory and is
+// rescaled only when a row's maximum has grown by more than 2^8 since the scale in use was chosen
+// (the final division by the row sum makes the choice of scale immaterial).  The scores of the
+// next page are issued before the probabilities of the current one are ready, and the two groups
+// alternate, so the tensor core works while the softmax runs.
+//
+// Values sit in the cache as [key][d]; they enter the second product as an MN-major operand, so
+// nothing is transposed.  Causal and window masks come from absolute positions; a prompt that
+// continues a cached prefix needs nothing special.  All barrier waits are bounded; a wait that
+// gives up sets a status word (gb_attention_tc5_status) and the CTA runs out.
+#include "tc5.cuh"
+
+#include <math.h>
+
+struct AttnParams {
+    const void* q;
+    int64_t q_row_stride;
+    void* out;
+    int64_t out_row_stride;
+    const void* k_plane;
+    const void* v_plane;
+    const int* block_table;
+    int bt_stride;
+    int ring_pages;
+    const int* seq_slot;
+    const int* seq_q_start;
+    const int* seq_q_len;
+    const int* seq_kv_len;
+    int nseq, heads, kv_heads, d;
+    int max_q_len;
+    float scale;
+    int window;
+    int num_splits;
+    float* scratch;
+};
+
+namespace {
+
+__device__ int g_status;
+
+typedef __nv_bfloat16 bf16;
+constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 3, THREADS = 352;
+constexpr int QPANEL = 128 * 128;               // 128 rows of 128 bytes (64 head elements)
+constexpr int KPANEL = 64 * 128;                // 64 keys of 128 bytes
+constexpr int Q_BYTES = 2 * QPANEL;             // one group's query tile
+constexpr int P_BYTES = 128 * 128;              // one group's probabilities: 128 rows x 64 keys
+constexpr int K_BYTES = 2 * KPANEL, V_BYTES = 2 * KPANEL, STAGE_BYTES = K_BYTES + V_BYTES;
+constexpr int TMEM_COLS = 512;                  // S: 2 groups x 2 buffers x 64; O: 2 groups x 128
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_AT = 8.0f;              // rescale O when the row maximum outgrew the scale by 2^8
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+
+// MN-major operand (values: rows are keys, 128-byte rows of 64 head elements, the second half of
+// the head one panel further): leading byte offset = panel, stride byte offset = 8 rows.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(KPANEL >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
+// 32 columns of this thread's lane without waiting for them (pair with tmem_wait_ld)
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+__global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                   const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
+    unsigned char* Ps = Qs + GROUPS * Q_BYTES;         // [GROUPS][2][P_BYTES]
+    unsigned char* KVs = Ps + GROUPS * 2 * P_BYTES;    // [STAGES][K | V]
+    __shared__ uint64_t q_full, kv_full[STAGES], kv_empty[STAGES];
+    __shared__ uint64_t s_full[GROUPS][2], p_full[GROUPS][2], o_done[GROUPS][2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_len = p.seq_q_len[seq], kv_len = p.seq_kv_len[seq];
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // long tiles first
+    const int q0 = qt * (GROUPS * BQ);
+    if (q0 >= q_len) return;  // the whole CTA leaves before anything is allocated
+    const int past = kv_len - q_len;
+    const int q_start = p.seq_q_start[seq];
+    const int G = p.heads / p.kv_heads, kvh = head / G;
+    const int* bt = p.block_table + (int64_t)p.seq_slot[seq] * p.bt_stride;
+
+    // pages each group walks: from the first page any of its rows may see to the page of its last row
+    int lo_pos = 0;
+    if (p.window > 0) {
+        lo_pos = past + q0 - p.window + 1;
+        if (lo_pos < 0) lo_pos = 0;
+    }
+    const int t_lo = lo_pos / BKV;
+    int n_g[GROUPS];
+#pragma unroll
+    for (int g = 0; g < GROUPS; g++) {
+        const int first = q0 + g * BQ;
+        if (first >= q_len) {
+            n_g[g] = 0;
+        } else {
+            const int last = (first + BQ < q_len ? first + BQ : q_len) - 1;
+            n_g[g] = (past + last) / BKV - t_lo + 1;
+        }
+    }
+    const int n = n_g[0] > n_g[1] ? n_g[0] : n_g[1];
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], GROUPS);  // one arrival from each group's issuing thread
+        }
+        for (int g = 0; g < GROUPS; g++) {
+            for (int b = 0; b < 2; b++) {
+                mbar_init(&s_full[g][b], 1);
+                mbar_init(&p_full[g][b], 4);
+                mbar_init(&o_done[g][b], 1);
+            }
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    // columns: S of group g, buffer b at g * 128 + b * 64; O of group g at 256 + g * 128
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, GROUPS * Q_BYTES);
+#pragma unroll
+            for (int g = 0; g < GROUPS; g++) {
+                tma_load_2d(Qs + g * Q_BYTES, &map_q, head * HD, q_start + q0 + g * BQ, &q_full);
+                tma_load_2d(Qs + g * Q_BYTES + QPANEL, &map_q, head * HD + 64, q_start + q0 + g * BQ, &q_full);
+            }
+            int issued = 0;
+            for (int j = 0; j < n; j++) {
+                const int s = j % STAGES;
+                const uint32_t phase = (uint32_t)(j / STAGES) & 1u;
+                if (!mbar_wait(&kv_empty[s], phase ^ 1u)) {
+                    atomicCAS(&g_status, 0, 1);
+                    abort_s = 1;
+                }
+                if (*(volatile int*)&abort_s) break;
+                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+                unsigned char* ks = KVs + (size_t)s * STAGE_BYTES;
+                unsigned char* vs = ks + K_BYTES;
+                int lp = t_lo + j;
+                if (lp >= p.bt_stride) lp = p.bt_stride - 1;
+                const int row = (bt[lp] * p.kv_heads + kvh) * 64;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    tma_load_2d(ks + h * KPANEL, &map_k, h * 64, row, &kv_full[s]);
+                    tma_load_2d(vs + h * KPANEL, &map_v, h * 64, row, &kv_full[s]);
+                }
+                issued = j + 1;
+            }
+            if (*(volatile int*)&abort_s) {
+                for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++)
+                    mbar_wait(&kv_full[j % STAGES], (uint32_t)(j / STAGES) & 1u);
+                mbar_wait(&q_full, 0);
+            }
+        }
+    } else if (warp <= GROUPS) {
+        // one issuing thread per group: waiting on a barrier and committing to one cost a few hundred
+        // cycles each on the issuing thread, so the groups do not share a thread
+        if (lane == 0) {
+            const int g = warp - 1;
+            const int my_n = n_g[g];
+            const uint32_t idesc_qk = instr_desc(BQ, BKV);
+            const uint32_t idesc_pv = instr_desc(BQ, HD) | (1u << 16);  // values enter MN-major
+            bool ok = mbar_wait(&q_full, 0);
+            int kv_seen = -1;  // last page whose arrival has been waited for
+            auto need_page = [&](int j) -> bool {
+                while (kv_seen < j) {
+                    kv_seen++;
+                    if (!mbar_wait(&kv_full[kv_seen % STAGES], (uint32_t)(kv_seen / STAGES) & 1u)) return false;
+                }
+                return true;
+            };
+            // descriptors are built once and only advanced by constants in the loops
+            const uint64_t q_desc = smem_desc(s32(Qs + g * Q_BYTES));
+            uint64_t p_desc[2], k_desc[STAGES], v_desc[STAGES];
+            p_desc[0] = smem_desc(s32(Ps + (g * 2) * P_BYTES));
+            p_desc[1] = smem_desc(s32(Ps + (g * 2 + 1) * P_BYTES));
+#pragma unroll
+            for (int s = 0; s < STAGES; s++) {
+                k_desc[s] = smem_desc(s32(KVs + (size_t)s * STAGE_BYTES));
+                v_desc[s] = smem_desc_mn(s32(KVs + (size_t)s * STAGE_BYTES + K_BYTES));
+            }
+            // S_g[j & 1] = Q_g K_j^T.  The buffer is free: the softmax read S of page j - 2 before it
+            // announced the probabilities of that page, and this thread waited for those.
+            auto scores = [&](int j) -> bool {
+                const int b = j & 1;
+                if (!need_page(j)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint64_t kd = k_desc[j % STAGES];
+                const uint32_t d_tmem = tmem_base + (uint32_t)(g * 128 + b * 64);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    // 64 head elements to a panel; 16 elements = 32 bytes = 2 address units inside it
+                    umma(d_tmem, q_desc + (uint64_t)((ks >> 2) * (QPANEL >> 4) + (ks & 3) * 2),
+                         kd + (uint64_t)((ks >> 2) * (KPANEL >> 4) + (ks & 3) * 2), idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[g][b]);
+                return true;
+            };
+            auto values = [&](int j) -> bool {  // O_g (+)= P_g[j & 1] V_j
+                const int b = j & 1;
+                if (!mbar_wait(&p_full[g][b], (uint32_t)(j >> 1) & 1u)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint64_t pd = p_desc[b], vd = v_desc[j % STAGES];
+                const uint32_t d_tmem = tmem_base + (uint32_t)(256 + g * 128);
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; kk++)  // 16 keys = 16 rows of 128 bytes further into the values
+                    umma(d_tmem, pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&o_done[g][b]);
+                return true;
+            };
+            if (ok && my_n > 0) ok = scores(0);
+            for (int j = 0; j < n && ok; j++) {
+                if (j + 1 < my_n) ok = scores(j + 1);
+                if (ok && j < my_n) ok = values(j);
+                // This group is done with page j.  A group with fewer pages only keeps the count, but
+                // it must not run ahead of the loads, or it would arrive twice in one phase.
+                if (ok && j >= my_n) ok = need_page(j);
+                if (ok) umma_commit(&kv_empty[j % STAGES]);
+            }
+            if (!ok) {
+                atomicCAS(&g_status, 0, 3);
+                abort_s = 1;
+            }
+        }
+    } else {
+        // softmax: group g, thread = query row
+        const int g = (warp - 1 - GROUPS) >> 2;
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;               // row within the group
+        const int qrow = q0 + g * BQ + r;             // row within the sequence's new rows
+        const int pos = past + qrow;                  // absolute position
+        const bool row_ok = qrow < q_len;
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        const uint32_t o_addr = tmem_base + lane_addr + (uint32_t)(256 + g * 128);
+        const float sc = p.scale * LOG2E;
+        const int my_n = n_g[g];
+        float m_run = -INFINITY;   // true running maximum (scaled, base 2)
+        float m_used = -INFINITY;  // the maximum the probabilities and O are currently scaled by
+        float l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < my_n && ok; j++) {
+            const int b = j & 1, key0 = (t_lo + j) * BKV;
+            if (!mbar_wait(&s_full[g][b], (uint32_t)(j >> 1) & 1u)) {
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(g * 128 + b * 64);
+            uint32_t v0[32], v1[32];
+            tmem_ld32_nowait(s_addr, v0);
+            tmem_ld32_nowait(s_addr + 32u, v1);
+            tmem_wait_ld();
+
+            const bool need_mask = key0 + BKV - 1 > pos || (p.window > 0 && key0 <= pos - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int ka = key0 + i, kb = key0 + 32 + i;
+                    if (ka > pos || (p.window > 0 && ka <= pos - p.window)) v0[i] = 0xff800000u;  // -inf
+                    if (kb > pos || (p.window > 0 && kb <= pos - p.window)) v1[i] = 0xff800000u;
+                }
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) mx[e] = fmaxf(mx[e], fmaxf(__uint_as_float(v0[i + e]), __uint_as_float(v1[i + e])));
+            }
+            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;  // sc > 0
+            m_run = fmaxf(m_run, tile_max);
+            // rescale only when the maximum has outgrown the scale in use (or there is none yet)
+            const bool grow = m_run > m_used + RESCALE_AT || (m_used == -INFINITY && m_run != -INFINITY);
+            // this page's probability buffer was read by the product of two pages ago
+            if (!mbar_wait(&o_done[g][b], ((uint32_t)(j >> 1) & 1u) ^ 1u)) {
+                ok = false;
+                break;
+            }
+            unsigned char* Pg = Ps + (g * 2 + b) * P_BYTES;
+            if (__any_sync(0xffffffffu, grow && j > 0)) {
+                // O_g may only be touched between products: wait for the previous page's
+                if (!mbar_wait(&o_done[g][(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                // the whole warp takes part (tensor-memory access is warp-wide); rows that keep their scale multiply by 1
+                const float f = (grow && j > 0) ? fast_exp2(m_used - m_run) : 1.f;  // m_used = -inf gives 0: O is all zeros then
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + (uint32_t)c0, o);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    tmem_st32(o_addr + (uint32_t)c0, o);
+                }
+                l *= f;
+            }
+            if (grow) m_used = m_run;
+            const float mbase = m_used == -INFINITY ? 0.f : m_used;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 8; c++) {  // eight 16-byte chunks of eight keys
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int i = (c & 3) * 8 + e * 2;
+                    const uint32_t a = c < 4 ? v0[i] : v1[i], bb = c < 4 ? v0[i + 1] : v1[i + 1];
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(a), sc, -mbase)), p1 = fast_exp2(fmaf(__uint_as_float(bb), sc, -mbase));
+                    sum[e] += p0 + p1;
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                    pk[e] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                // K-major operand rows of 128 bytes (64 keys), groups of 8 rows, 128-byte swizzle
+                unsigned char* dst = Pg + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[g][b]);
+        }
+        if (ok && my_n > 0 && !mbar_wait(&o_done[g][(my_n - 1) & 1], (uint32_t)((my_n - 1) >> 1) & 1u)) ok = false;
+        if (!ok) {
+            atomicCAS(&g_status, 0, 4);
+            abort_s = 1;
+        } else if (my_n > 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float inv = 1.f / l;
+            bf16* op = (bf16*)p.out + (int64_t)(q_start + qrow) * p.out_row_stride + (int64_t)head * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(o_addr + (uint32_t)c0, o);
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 o4;
+                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                        o4.x = *reinterpret_cast<uint32_t*>(&a0);
+                        o4.y = *reinterpret_cast<uint32_t*>(&a1);
+                        o4.z = *reinterpret_cast<uint32_t*>(&a2);
+                        o4.w = *reinterpret_cast<uint32_t*>(&a3);
+                        *reinterpret_cast<uint4*>(op + c0 + i) = o4;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// 2-D map over `rows` rows of `cols` bfloat16 with a row stride of ld elements; boxes of box_rows x 64
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int cols, int64_t ld, int box_rows) {
+    Tc5EncodeTiledFn fn = tc5_encode_fn();
+    if (!fn) GB_REFUSE("attention_tc5: the driver offers no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) GB_REFUSE("attention_tc5: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+}  // namespace
+
+// rows: packed query rows in the q buffer; pages: pages in each cache plane
+GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, cudaStream_t stream) {
+    AttnParams p = *pp;
+    if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
+    const char* who = "attention_prefill_tc5";
+    if (p.d != HD) GB_REFUSE("%s: head_dim %d; this kernel takes 128", who, p.d);
+    if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("%s: %d heads over %d kv heads", who, p.heads, p.kv_heads);
+    if (p.num_splits != 1) GB_REFUSE("%s: key splits are for single-token rows", who);
+    if (p.ring_pages != 0) GB_REFUSE("%s: ring storage is not supported by this kernel", who);
+    if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
+    if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
+    if (((uintptr_t)p.out & 15) || (p.out_row_stride & 7)) GB_REFUSE("%s: output rows must be 16-byte aligned", who);
+    if (((uintptr_t)p.k_plane & 15) || ((uintptr_t)p.v_plane & 15)) GB_REFUSE("%s: cache planes must be 16-byte aligned", who);
+    if (rows <= 0 || pages <= 0) GB_REFUSE("%s: %d rows, %d pages", who, rows, pages);
+    if ((int64_t)pages * p.kv_heads * 64 > 0x7fffffff) GB_REFUSE("%s: the cache plane has too many rows for one tensor map", who);
+    const int smem = GROUPS * (Q_BYTES + 2 * P_BYTES) + STAGES * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) GB_REFUSE("%s: cannot reserve %d bytes of shared memory: %s", who, smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_q, map_k, map_v;
+    if (int rc = make_map(&map_q, p.q, rows, p.heads * HD, p.q_row_stride, BQ)) return rc;
+    if (int rc = make_map(&map_k, p.k_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
+    if (int rc = make_map(&map_v, p.v_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
+    dim3 grid(ceil_div(p.max_q_len, GROUPS * BQ), p.heads, p.nseq);
+    if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
+    attn_prefill_tc5_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+    GB_CHECK_LAUNCH("attention_prefill_tc5");
+    return 0;
+}
+
+GB_API int gb_attention_tc5_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return v;
+}

@@ -37,6 +37,7 @@ SOURCES = [
     "gemm_tc5_decode.cu",
     "attention_simt.cu",
     "attention_mma.cu",
+    "attention_tc5.cu",
     "sampling.cu",
     "no_alloc.cu",
 ]

@@ -262,7 +262,7 @@ def tc5_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 def tc5_status() -> int:
     """0, or which role of a tcgen05 kernel gave up waiting on a barrier since the last call."""
     code = 0
-    for name in ("gb_gemm_tc5_status", "gb_gemm_tc5_decode_status"):
+    for name in ("gb_gemm_tc5_status", "gb_gemm_tc5_decode_status", "gb_attention_tc5_status"):
         if _has(name):
             code = code or int(getattr(_lib, name)())
     return code
@@ -330,6 +330,11 @@ class _AttnParams(Structure):
     ]
 
 
+# prompts whose longest sequence brings at least this many rows use the tcgen05 attention kernel
+# (tiles of 128 query rows); shorter ones the mma.sync kernel (tiles of 64)
+TC5_ATTENTION_MIN_ROWS = 65
+
+
 def attention_scratch_floats(nseq: int, heads: int, head_dim: int, num_splits: int) -> int:
     return nseq * heads * num_splits * (head_dim + 2)
 
@@ -370,6 +375,9 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
         if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and (head_dim <= 128 or head_dim == 256) and ring_pages == 0:
             if max_q_len == 1 and _has("gb_attention_decode_mma"):
                 algo = "decode_mma"
+            elif (max_q_len >= TC5_ATTENTION_MIN_ROWS and head_dim == 128 and _has("gb_attention_prefill_tc5")
+                  and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0):
+                algo = "prefill_tc5"
             elif max_q_len > 1 and _has("gb_attention_prefill_mma"):
                 algo = "prefill_mma"
     nk = 2 if num_splits > 1 else 1
@@ -379,6 +387,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
         _check(_lib.gb_attention_decode_mma(byref(p), _stream()), nk)
     elif algo == "prefill_mma":
         _check(_lib.gb_attention_prefill_mma(byref(p), _stream()))
+    elif algo == "prefill_tc5":
+        _check(_lib.gb_attention_prefill_tc5(byref(p), c_int(q.shape[0]), c_int(k_plane.shape[0]), _stream()))
     else:
         raise KernelError(f"attention: unknown algorithm '{algo}'")
     return algo

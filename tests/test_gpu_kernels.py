@@ -305,9 +305,23 @@ def test_attention_prompts(ops, dtype, algo, heads, kvh, d):
     out, ref, used = attention_case(ops, dtype, heads, kvh, d, q_lens=[70, 5, 1, 33], kv_lens=[70, 69, 130, 33], algo=algo)
     close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
     if algo == "auto":
-        assert used == "prefill_mma"
+        assert used == ("prefill_tc5" if d == 128 else "prefill_mma")
     out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens=[200, 130], kv_lens=[200, 333], algo=algo, seed=3)
     close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+    assert ops.tc5_status() == 0
+
+
+@pytest.mark.parametrize("algo", ["prefill_tc5", "prefill_mma"])
+@pytest.mark.parametrize("heads,kvh", [(4, 1), (3, 3), (32, 8)])
+def test_attention_prompts_head_dim_128_both_tensor_core_kernels(ops, algo, heads, kvh):
+    """The tcgen05 kernel (tiles of 128 rows, two pages a step) and the mma.sync kernel on the same
+    cases: lengths around the tile and page sizes, prompts that continue a cached prefix, a window."""
+    for q_lens, kv_lens, window in (([128], [128], 0), ([129, 1, 64], [129, 300, 64], 0), ([257, 100], [257, 612], 0),
+                                    ([300], [700], 150), ([65], [65], 7)):
+        out, ref, used = attention_case(ops, torch.bfloat16, heads, kvh, 128, q_lens, kv_lens, window=window, algo=algo, seed=11)
+        assert used == algo
+        close(out, ref, 1.2e-2)
+    assert ops.tc5_status() == 0
 
 
 @pytest.mark.parametrize("dtype,algo", KINDS)
