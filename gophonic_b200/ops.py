@@ -146,6 +146,10 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2) or out.stride(1) != 1 or not gemm_swiglu_accepts(a, w):
         raise KernelError(f"gemm_swiglu: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if M >= TC5_PAIR_MIN_ROWS and algo != "tc5" and _has("gb_gemm_tc5_pair_swiglu") or algo == "tc5_pair":
+        _check(_lib.gb_gemm_tc5_pair_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                            c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+        return
     if M > 64:
         _check(_lib.gb_gemm_tc5_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                        c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
@@ -208,6 +212,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
             algo = "tc5_decode"
         elif M <= 64 and _has("gb_gemm_skinny"):
             algo = "skinny"
+        elif _has("gb_gemm_tc5_pair") and M >= TC5_PAIR_MIN_ROWS and tc5_accepts(a, w, out):
+            algo = "tc5_pair"
         elif _has("gb_gemm_tc5") and M >= 128 and tc5_accepts(a, w, out):
             algo = "tc5"
         elif _has("gb_gemm_mma"):
@@ -223,6 +229,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     elif algo == "tc5":
         _check(_lib.gb_gemm_tc5(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                 c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    elif algo == "tc5_pair":
+        _check(_lib.gb_gemm_tc5_pair(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                     c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
     elif algo == "tc5_decode":
         _tc5_decode(a, w, out, 0)
     elif algo == "simt":
@@ -232,6 +241,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     return algo
 
 
+# rows from which the tcgen05 kernel that pairs two SMs on tiles of 256 x 256 is used
+TC5_PAIR_MIN_ROWS = 192
 # rows up to which the fragment-streaming kernel is used for decode; above it (to 64) the tcgen05
 # split-K kernel takes over
 SKINNY_MAX_ROWS = 8

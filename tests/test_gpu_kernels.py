@@ -101,7 +101,7 @@ def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
     g, u = x.double() @ gate.double().T, x.double() @ up.double().T
     ref = g / (1 + torch.exp(-g)) * u
     assert ops.gemm_swiglu_accepts(x, w)
-    for algo in (("skinny", "tc5_decode") if M <= 64 else ("tc5",)):
+    for algo in (("skinny", "tc5_decode") if M <= 64 else ("tc5", "tc5_pair")):
         out = torch.full((M, inter), float("nan"), dtype=out_dtype, device=DEV)
         ops.gemm_swiglu(x, w, out, algo=algo)
         close(out, ref, 2e-5 if out_dtype == torch.float32 else 6e-3)
@@ -136,7 +136,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
     assert torch.equal(one[0], full[67])
 
 
-@pytest.mark.parametrize("algo", ["skinny", "mma", "tc5", "tc5_decode"])
+@pytest.mark.parametrize("algo", ["skinny", "mma", "tc5", "tc5_pair", "tc5_decode"])
 @pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (300, 1000, 512), (2048, 512, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
@@ -148,7 +148,7 @@ def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
         with pytest.raises(ops.KernelError):
             ops.gemm(a, w, out, algo=algo)
         return
-    if algo == "tc5" and not ops.tc5_accepts(a, w, out):
+    if algo in ("tc5", "tc5_pair") and not ops.tc5_accepts(a, w, out):
         with pytest.raises(ops.KernelError):
             ops.gemm(a, w, out, algo=algo)
         return
