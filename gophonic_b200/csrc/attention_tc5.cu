@@ -124,9 +124,11 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     __shared__ int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // heads vary fastest and the longest tiles of all heads come first, so the SMs that finish a
+    // long tile early pick up the short ones (tiles of a causal prompt differ eightfold in work)
+    const int seq = blockIdx.z, head = blockIdx.x;
     const int q_len = p.seq_q_len[seq], kv_len = p.seq_kv_len[seq];
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // long tiles first
+    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int q0 = qt * (GROUPS * BQ);
     if (q0 >= q_len) return;  // the whole CTA leaves before anything is allocated
     const int past = kv_len - q_len;
@@ -466,7 +468,7 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (int rc = make_map(&map_q, p.q, rows, p.heads * HD, p.q_row_stride, BQ)) return rc;
     if (int rc = make_map(&map_k, p.k_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
     if (int rc = make_map(&map_v, p.v_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
-    dim3 grid(ceil_div(p.max_q_len, GROUPS * BQ), p.heads, p.nseq);
+    dim3 grid(p.heads, ceil_div(p.max_q_len, GROUPS * BQ), p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
     attn_prefill_tc5_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_k, map_v, p);
     GB_CHECK_LAUNCH("attention_prefill_tc5");
