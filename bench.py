@@ -183,7 +183,7 @@ def probe(name):
         M, N, K = 2048, 24576, 4096       # gate/up of one layer: 201 MB of weights
         a, w = rnd(M, K), rnd(N, K, scale=0.05)
         out = torch.empty((M, N // 2 if name.endswith("swiglu") else N), dtype=bf, device=dev)
-        fn = (lambda: ops.gemm_swiglu(a, w, out)) if name.endswith("swiglu") else (lambda: ops.gemm(a, w, out, algo="tc5"))
+        fn = (lambda: ops.gemm_swiglu(a, w, out)) if name.endswith("swiglu") else (lambda: ops.gemm(a, w, out))
         work = 2.0 * M * N * K
         unit = "TFLOP/s"
     elif name in ("gemm_decode_b8", "gemm_decode_b64"):
@@ -225,6 +225,30 @@ def probe(name):
             work, unit = 2.0 * n_pages * kvh * 64 * d * 2, "GB/s"
         else:
             work, unit = 2.0 * heads * d * q_len * q_len, "TFLOP/s"
+    elif name in ("prefill_step", "decode_step"):
+        # a whole engine step of a 4-layer model with the layer sizes of the benchmark: the launch
+        # list of a profiler then shows every kernel of a layer with its share
+        from gophonic_b200.config import Qwen3Config
+        from gophonic_b200.engine import Engine, Model
+        cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=8,
+                          head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=40960,
+                          rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+        model = Model.from_random(cfg, seed=0, dtype="bfloat16", device=dev)
+        engine = Engine(model, max_tokens=8 * CONTEXT, max_slots=8, max_seq_tokens=CONTEXT)
+        prompt = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(1)).tolist()
+        if name == "prefill_step":
+            def fn():
+                slot = engine.new_sequence()
+                engine.step([(slot, prompt)])
+                engine.end_sequence(slot)
+            work, unit = float(PREFILL_TOKENS), "tok/s"
+        else:
+            fill_cache_random(engine, torch)
+            slots = decode_setup(engine, 8, CONTEXT - 64, torch)
+
+            def fn():
+                engine.step([(s, [1]) for s in slots])
+            work, unit = 8.0, "tok/s"
     else:
         raise SystemExit(f"unknown probe '{name}'")
     for _ in range(3):
@@ -237,7 +261,7 @@ def probe(name):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / 3
-    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    rate = work / (ms * 1e-3) / {"TFLOP/s": 1e12, "GB/s": 1e9}.get(unit, 1.0)
     print(json.dumps({"probe": name, "ms": round(ms, 4), "rate": round(rate, 1), "unit": unit, "status": ops.tc5_status()}))
     return 0
 

@@ -238,6 +238,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [16][SD]
     bf16* KV = Qs + 16 * SD;                          // [DSTAGES][2][64][SD]
 
+    pdl_wait();
     pdl_trigger();  // the product that follows may start fetching its weights
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int G = p.heads / p.kv_heads;
@@ -465,7 +466,13 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     const int hchunks = (G + GC - 1) / GC;
     dim3 grid(p.num_splits, p.kv_heads * hchunks, p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("attention_decode_mma: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
-    attn_decode_mma_kernel<HD, QREG><<<grid, 128, smem, stream>>>(p);
+    // Measured at 8 and 64 sequences of 4096 keys: launched early, this kernel gains a little when it
+    // is alone (one split, many CTAs) and loses when its CTAs and those of the merge behind it sit
+    // waiting beside the kernels ahead, so only the single-split form is a dependent launch.
+    if (p.num_splits == 1)
+        launch_pdl(attn_decode_mma_kernel<HD, QREG>, grid, dim3(128), (size_t)smem, stream, p);
+    else
+        attn_decode_mma_kernel<HD, QREG><<<grid, 128, smem, stream>>>(p);
     GB_CHECK_LAUNCH("attention_decode_mma");
     if (p.num_splits > 1)
         return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, p.d,

@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t out_row_stride,
                                   const int* __restrict__ seq_q_start, int heads, int d, int num_splits) {
+    pdl_wait();
     pdl_trigger();  // the product that follows may start fetching its weights
     int head = blockIdx.x, seq = blockIdx.y;
     const float* sp = scratch + ((int64_t)seq * heads + head) * num_splits * (d + 2);

@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     __shared__ int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();  // the tile's extent comes from the step's metadata
+    pdl_trigger();
     // heads vary fastest and the longest tiles of all heads come first, so the SMs that finish a
     // long tile early pick up the short ones (tiles of a causal prompt differ eightfold in work)
     const int seq = blockIdx.z, head = blockIdx.x;
@@ -470,8 +472,8 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (int rc = make_map(&map_v, p.v_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
     dim3 grid(p.heads, ceil_div(p.max_q_len, GROUPS * BQ), p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
-    attn_prefill_tc5_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_k, map_v, p);
-    GB_CHECK_LAUNCH("attention_prefill_tc5");
+    cudaError_t e = launch_pdl(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p);
+    if (e != cudaSuccess) GB_REFUSE("%s: launch failed: %s", who, cudaGetErrorString(e));
     return 0;
 }
 

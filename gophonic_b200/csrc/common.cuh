@@ -72,9 +72,12 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
 // may begin while the kernel before it on the stream is still running; it must call pdl_wait()
-// before it touches anything that kernel writes (or writes anything that kernel reads).  A kernel
-// calls pdl_trigger() once the kernel after it may begin its independent prologue.  Both are
-// no-ops for ordinary launches.
+// before it touches anything that an earlier kernel or copy of the stream writes (or writes
+// anything one of them reads): before the wait it may use only its parameters and memory that
+// never changes (weights).  Every CTA calls pdl_wait(), also one that has nothing to do, so that
+// a kernel never completes before the kernel ahead of it.  A kernel calls pdl_trigger() once the
+// kernel after it may begin its own prologue; the kernels here do so after their own wait, so at
+// most two kernels overlap.  Both calls are no-ops for ordinary launches.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
@@ -91,5 +94,26 @@ static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 b
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The same for a kernel whose CTAs form thread-block clusters of cluster_x x cluster_y.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                             unsigned cluster_x, unsigned cluster_y, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster_x;
+    attr[1].val.clusterDim.y = cluster_y;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_vec_kernel(float* __restr
                                                                   const int* __restrict__ row_index) {
     __shared__ float warp_part[THREADS / 32];
     __shared__ float inv_s;
+    pdl_wait();
     pdl_trigger();  // the product that follows may start fetching its weights
     const int orow = blockIdx.x;
     const int row = row_index ? row_index[orow] : orow;
@@ -166,14 +167,14 @@ GB_API int gb_add_rmsnorm(float* h, const float* delta, const float* w, float ep
     if ((n & 3) == 0 && n <= 1024 * 16 && aligned) {
         if (n <= 256 * 16) {
             if (out_dtype == GB_F32)
-                add_rmsnorm_vec_kernel<float, 256><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (float*)out, row_index);
+                launch_pdl(add_rmsnorm_vec_kernel<float, 256>, dim3(out_rows), dim3(256), 0, stream, h, delta, w, eps, n, (float*)out, row_index);
             else
-                add_rmsnorm_vec_kernel<__nv_bfloat16, 256><<<out_rows, 256, 0, stream>>>(h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
+                launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16, 256>, dim3(out_rows), dim3(256), 0, stream, h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
         } else {
             if (out_dtype == GB_F32)
-                add_rmsnorm_vec_kernel<float, 1024><<<out_rows, 1024, 0, stream>>>(h, delta, w, eps, n, (float*)out, row_index);
+                launch_pdl(add_rmsnorm_vec_kernel<float, 1024>, dim3(out_rows), dim3(1024), 0, stream, h, delta, w, eps, n, (float*)out, row_index);
             else
-                add_rmsnorm_vec_kernel<__nv_bfloat16, 1024><<<out_rows, 1024, 0, stream>>>(h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
+                launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16, 1024>, dim3(out_rows), dim3(1024), 0, stream, h, delta, w, eps, n, (__nv_bfloat16*)out, row_index);
         }
         GB_CHECK_LAUNCH("add_rmsnorm");
         return 0;
@@ -366,6 +367,8 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
 // The common geometry (bfloat16, head_dim 128 rotated in full): a warp per (row, head), every lane
 // holds four consecutive elements, so element i and its partner i + 64 sit in lanes l and l ^ 16.
 __global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) {
+    pdl_wait();
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x;
     const int head = blockIdx.y * 8 + warp;
@@ -431,7 +434,7 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     if (dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
         !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
         ceil_div(total_heads, 8) <= 65535) {
-        qk_rope_bf16_d128_kernel<<<dim3(p.rows, ceil_div(total_heads, 8)), 256, 0, stream>>>(p);
+        launch_pdl(qk_rope_bf16_d128_kernel, dim3(p.rows, ceil_div(total_heads, 8)), dim3(256), 0, stream, p);
         GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
         return 0;
     }

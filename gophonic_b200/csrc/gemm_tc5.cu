@@ -146,6 +146,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();  // barriers and tensor memory were set up while the kernel ahead was still running
+    pdl_trigger();
 
     // A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tiles are numbered with the M tile
     // fastest, so CTAs that run together share their W slabs.
@@ -344,6 +346,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
     cluster_sync_all();  // the other CTA's barriers are initialised before anything signals them
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();  // barriers and tensor memory were set up while the kernel ahead was still running
+    pdl_trigger();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -477,19 +481,8 @@ int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int6
     const int64_t total = (int64_t)ceil_div(M, 256) * ceil_div(N, 256);
     if (total > 0x7fffffff) GB_REFUSE("gemm_tc5_pair: %lld tiles are too many", (long long)total);
     const int pairs = total < sms / 2 ? (int)total : sms / 2;  // one pair of CTAs per pair of SMs walks the tiles
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc5_pair_kernel<TC>, map_a, map_w, (TC*)C, M, N, K, ldc, epi);
+    cudaError_t e = launch_pdl_cluster(gemm_tc5_pair_kernel<TC>, dim3(2 * pairs), dim3(THREADS), (size_t)smem, stream, 2, 1, map_a, map_w,
+                                       (TC*)C, M, N, K, ldc, epi);
     if (e != cudaSuccess) GB_REFUSE("gemm_tc5_pair: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -515,8 +508,8 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
     const int64_t total = (int64_t)ceil_div(M, BM) * ceil_div(N, BN);
     if (total > 0x7fffffff) GB_REFUSE("gemm_tc5: %lld tiles are too many", (long long)total);
     const int grid = total < sms ? (int)total : sms;  // one CTA per SM walks the tiles
-    gemm_tc5_kernel<TC><<<grid, THREADS, smem, stream>>>(map_a, map_w, (TC*)C, M, N, K, ldc, epi);
-    GB_CHECK_LAUNCH("gemm_tc5");
+    cudaError_t e = launch_pdl(gemm_tc5_kernel<TC>, dim3(grid), dim3(THREADS), (size_t)smem, stream, map_a, map_w, (TC*)C, M, N, K, ldc, epi);
+    if (e != cudaSuccess) GB_REFUSE("gemm_tc5: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
 

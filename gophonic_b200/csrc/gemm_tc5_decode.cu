@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_decode_kernel(const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();  // barriers and tensor memory were set up while the kernel ahead was still running
+    pdl_trigger();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -224,19 +226,8 @@ int launch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t l
     while (splits > 1 && KB < splits) splits >>= 1;
     const int kb_per_split = ceil_div(KB, splits);
     if (tiles > MAX_TILES) GB_REFUSE("gemm_tc5_decode: N = %d exceeds %d tiles", N, MAX_TILES);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles, splits);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = splits;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc5_decode_kernel<TC, NB>, map_w, map_x, (TC*)Y, M, N, K, ldy, splits, kb_per_split, epi);
+    cudaError_t e = launch_pdl_cluster(gemm_tc5_decode_kernel<TC, NB>, dim3(tiles, splits), dim3(THREADS), (size_t)smem, stream, 1,
+                                       (unsigned)splits, map_w, map_x, (TC*)Y, M, N, K, ldy, splits, kb_per_split, epi);
     if (e != cudaSuccess) GB_REFUSE("gemm_tc5_decode: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
