@@ -11,12 +11,9 @@
 // fixed order through shared memory, so results do not depend on the batch around a row.
 #include "mma.cuh"
 
-#include <stdlib.h>
-
 namespace {
 
-int g_max_kw = 0;      // most warps that split K inside a CTA (0: chosen by shape)
-int g_min_steps = 4;   // fewest 32-wide K steps a warp should own
+constexpr int MIN_STEPS = 4;  // fewest 32-wide K steps a warp should own
 
 template <int MT>  // MT tiles of 8 batch rows
 __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
@@ -150,39 +147,20 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
            cudaStream_t stream) {
     int steps = ceil_div(K, 32);
     // Few weight tiles (narrow outputs) leave SMs short of loads in flight: give each CTA more warps.
-    int max_kw = g_max_kw;
-    if (max_kw == 0) max_kw = (ceil_div(N, 16) <= 320 && MT <= 4) ? 16 : 8;
+    const int max_kw = (ceil_div(N, 16) <= 320 && MT <= 4) ? 16 : 8;
     int kw = 1;
-    while (kw < max_kw && steps / (kw * 2) >= g_min_steps) kw *= 2;
+    while (kw < max_kw && steps / (kw * 2) >= MIN_STEPS) kw *= 2;
     int k_per_warp = ceil_div(steps, kw) * 32;
     size_t smem = (size_t)kw * 16 * MT * 8 * sizeof(float);
-    static int mode = -1;  // experiment switch: bit 0 programmatic launch
-    if (mode < 0) {
-        const char* m = getenv("GB_SKINNY_MODE");
-        mode = m ? atoi(m) : 1;
-    }
-    if (mode & 1) {
-        cudaError_t e = launch_pdl(gemm_skinny_kernel<MT>, dim3(ceil_div(N, 16)), dim3(kw * 32), smem, stream, (const __nv_bfloat16*)X,
-                                   (const __nv_bfloat16*)W, Y, (int)(c_dtype == GB_BF16), M, N, K, ldx, ldy, k_per_warp, epi);
-        if (e != cudaSuccess) GB_REFUSE("gemm_skinny: launch failed: %s", cudaGetErrorString(e));
-        return 0;
-    }
-    gemm_skinny_kernel<MT><<<ceil_div(N, 16), kw * 32, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, Y,
-                                                                      c_dtype == GB_BF16, M, N, K, ldx, ldy, k_per_warp, epi);
-    GB_CHECK_LAUNCH("gemm_skinny");
+    // a programmatic dependent launch: the kernel requests its first weights before it waits for
+    // the kernel ahead of it
+    cudaError_t e = launch_pdl(gemm_skinny_kernel<MT>, dim3(ceil_div(N, 16)), dim3(kw * 32), smem, stream, (const __nv_bfloat16*)X,
+                               (const __nv_bfloat16*)W, Y, (int)(c_dtype == GB_BF16), M, N, K, ldx, ldy, k_per_warp, epi);
+    if (e != cudaSuccess) GB_REFUSE("gemm_skinny: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
 
 }  // namespace
-
-// Tuning knobs for measurements: most K-splitting warps per CTA (a power of two, at most 16) and the
-// fewest 32-wide steps a warp should own.
-GB_API int gb_gemm_skinny_tune(int max_kw, int min_steps) {
-    if (max_kw < 0 || max_kw > 16 || (max_kw & (max_kw - 1)) || min_steps < 1) GB_REFUSE("gemm_skinny_tune: (%d, %d)", max_kw, min_steps);
-    g_max_kw = max_kw;
-    g_min_steps = min_steps;
-    return 0;
-}
 
 static int skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, int epi,
                   cudaStream_t stream) {

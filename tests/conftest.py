@@ -43,6 +43,12 @@ def tiny_configs():
         "C": Qwen3Config(hidden_size=80, num_hidden_layers=1, num_attention_heads=5, num_key_value_heads=1,
                          head_dim=48, intermediate_size=136, vocab_size=333, max_position_embeddings=768,
                          rms_norm_eps=3e-6, rope_theta=50000.0, tie_word_embeddings=False),
+        # head_dim 128 and widths that reach the kernels the full-size model runs on: the tcgen05
+        # attention (prompts of 65 rows and more), the head_dim-128 rotation kernel, the tiled
+        # tcgen05 GEMMs (128 rows and more) and the tcgen05 decode GEMM (9 to 64 rows)
+        "D": Qwen3Config(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         head_dim=128, intermediate_size=520, vocab_size=2000, max_position_embeddings=1024,
+                         rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False),
     }
 
 

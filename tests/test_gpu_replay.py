@@ -58,11 +58,11 @@ def references(plain_models):
     return get
 
 
-LENGTHS = {"A": [1, 5, 17, 70, 131], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 129]}
+LENGTHS = {"A": [1, 5, 17, 70, 131], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 129], "D": [1, 64, 65, 130, 200, 300, 520]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "A32"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "A32"])
 def test_each_request_alone_and_whole(engines, references, plain_models, name, dtype):
     eng = engines(name, dtype)
     cfg, _ = plain_models[name]
@@ -80,7 +80,7 @@ def test_each_request_alone_and_whole(engines, references, plain_models, name, d
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_tokens_one_by_one(engines, references, plain_models, name, dtype):
     eng = engines(name, dtype)
     cfg, _ = plain_models[name]
@@ -101,7 +101,7 @@ def test_last_32_tokens_one_by_one(engines, references, plain_models, name, dtyp
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_batches_of_unequal_lengths_one_after_another(engines, references, plain_models, name, dtype):
     """Each batch starts together with unequal prompts, then one token each; shorter requests end
     earlier; the next batch reuses the slots and pages the last one gave back."""
@@ -152,6 +152,45 @@ def test_batches_of_unequal_lengths_one_after_another(engines, references, plain
         eng.cache.check()
         assert eng.cache.pages.held() == 0 and eng.cache.slots.held() == 0
     assert seen_slots[0] & seen_slots[1], "slots are used again"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wide_batch_on_the_full_size_kernels(engines, references, plain_models, dtype):
+    """Twenty requests of head_dim 128 that start together: prompts from 1 to 300 tokens in one step
+    (more than 192 rows: the paired-SM GEMM; prompts of 65 rows and more on the tcgen05 attention
+    next to short ones), then one token each for the 9-to-64-row decode GEMM, the shorter requests
+    ending earlier."""
+    eng = engines("D", dtype, 8192)
+    cfg, _ = plain_models["D"]
+    rng = np.random.default_rng(21)
+    plan = [(int(p), int(d)) for p, d in zip([1, 2, 7, 33, 63, 64, 65, 66, 100, 127, 128, 129, 190, 200, 256, 257, 300, 5, 70, 90],
+                                              rng.integers(1, 9, size=20))]
+    toks = [rng.integers(0, cfg["vocab_size"], size=p + d).tolist() for p, d in plan]
+    slots = [eng.new_sequence() for _ in plan]
+    got = [[] for _ in plan]
+    first = eng.step([(slots[i], toks[i][:p]) for i, (p, _) in enumerate(plan)], [list(range(p)) for p, _ in plan]).cpu().numpy()
+    o = 0
+    for i, (p, _) in enumerate(plan):
+        got[i].append(first[o:o + p])
+        o += p
+    for step in range(max(d for _, d in plan)):
+        live = [i for i in range(len(plan)) if step < plan[i][1]]
+        out = eng.step([(slots[i], [toks[i][plan[i][0] + step]]) for i in live], [[0]] * len(live)).cpu().numpy()
+        for j, i in enumerate(live):
+            got[i].append(out[j:j + 1])
+        for i in live:
+            if step + 1 >= plan[i][1]:
+                eng.end_sequence(slots[i])
+    from gophonic_b200 import ops
+    assert ops.tc5_status() == 0
+    for i, (p, d) in enumerate(plan):
+        ref = references("D", toks[i])
+        g = np.concatenate(got[i], 0)
+        err = np.max(np.abs(g - ref), axis=-1) / np.max(np.abs(ref))
+        bad = np.nonzero(err >= TOL[dtype])[0]
+        assert bad.size == 0, f"request {i} (prompt {p}, decoded {d}): first wrong position {bad[0]}, error {err[bad[0]]:.3g}"
+    eng.cache.check()
+    assert eng.cache.pages.held() == 0 and eng.cache.slots.held() == 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -269,7 +308,7 @@ def test_refused_steps_leave_the_cache_as_it_was(engines, plain_models):
     held = eng.cache.pages.held()
     for bad, exc, word in [([(s, [cfg["vocab_size"]])], StepError, "outside"), ([(s, [])], StepError, "no tokens"),
                            ([(s, [1]), (s, [2])], StepError, "twice"), ([(99, [1])], StepError, "not live"),
-                           ([(s, [1] * 300)], (StepError, CacheFull), "")]:
+                           ([(s, [1] * 300)], (StepError, CacheFull), None)]:
         with pytest.raises(exc, match=word):
             eng.step(bad)
         assert eng.length(s) == 3 and eng.cache.pages.held() == held
