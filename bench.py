@@ -26,6 +26,14 @@ sys.path.insert(0, ROOT)
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 
+# layer sizes by name: the default is the configuration the headline metric is quoted on; the
+# others are further points (--model), never the default
+SIZES = {
+    "8b": dict(layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, intermediate=12288, vocab=151936, tied=False),
+    "1.7b": dict(layers=28, hidden=2048, heads=16, kv_heads=8, head_dim=128, intermediate=6144, vocab=151936, tied=True),
+    "32b": dict(layers=64, hidden=5120, heads=64, kv_heads=8, head_dim=128, intermediate=25600, vocab=151936, tied=False),
+}
+
 
 def peaks():
     """(hbm GB/s, bf16 TFLOP/s burst, which) from MEASURED_PEAKS.json, else the stated fallback."""
@@ -104,7 +112,7 @@ def fill_cache_random(engine, torch):
 def time_decode(engine, sampler, batch, steps, warmup, torch, ops, e2e):
     """Returns (ms per step on the device, ms per step wall for the host-in/host-out loop, launches per step, h2d, d2h)."""
     import numpy as np
-    start_len = CONTEXT - (steps + warmup) - 1
+    start_len = engine.capacity - (steps + warmup) - 1
     slots = decode_setup(engine, batch, start_len, torch)
     rng = np.random.default_rng(0)
     tokens = rng.integers(0, engine.vocab, size=batch).tolist()
@@ -275,6 +283,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes (default: the benchmark's own, 8b)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length each sequence is filled to")
     ap.add_argument("--probe", default="", help="run one kernel on a small fixed workload (for profilers) and exit")
     args = ap.parse_args()
     if args.probe:
@@ -294,15 +304,18 @@ def main():
     from gophonic_b200.engine import Engine, Model
     from gophonic_b200.sampling import DeviceSampler
 
-    full_layers = 36
+    sz = SIZES[args.model]
+    context = args.context
+    full_layers = sz["layers"]
     layers = args.layers or full_layers
-    cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8,
-                      head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=40960,
-                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    cfg = Qwen3Config(hidden_size=sz["hidden"], num_hidden_layers=layers, num_attention_heads=sz["heads"],
+                      num_key_value_heads=sz["kv_heads"], head_dim=sz["head_dim"], intermediate_size=sz["intermediate"],
+                      vocab_size=sz["vocab"], max_position_embeddings=max(40960, context), rms_norm_eps=1e-6, rope_theta=1e6,
+                      tie_word_embeddings=sz["tied"])
     hbm_peak, tflops_peak, which = peaks()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    engine = Engine(model, max_tokens=max_batch * CONTEXT, max_slots=max_batch, max_seq_tokens=CONTEXT)
+    engine = Engine(model, max_tokens=max_batch * context, max_slots=max_batch, max_seq_tokens=context)
     fill_cache_random(engine, torch)
     sampler = DeviceSampler(cfg.vocab_size, max_batch, engine.device)
     weight_bytes = model.weight_bytes_per_step()
@@ -318,14 +331,15 @@ def main():
     achieved = step_bytes / (dev["ms"] * 1e-3) / 1e9
     value = args.batch / (dev["ms"] * 1e-3)
     line = {
-        "metric": "Qwen3-8B decode tok/s @ batch 8, context 4096 (random weights, bf16)",
+        "metric": f"Qwen3-{args.model.upper()} decode tok/s @ batch {args.batch}, context {context} (random weights, bf16)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(dev["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, random token ids, cache pre-filled with random keys/values",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B-shaped", "layers": layers, "layers_full": full_layers, "hidden": 4096, "heads": 32,
-                   "kv_heads": 8, "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "parallelism": "single-gpu", "l2": "step reads >15 GB of weights, larger than L2",
+        "config": {"model": f"Qwen3-{args.model.upper()}-shaped", "layers": layers, "layers_full": full_layers, "hidden": sz["hidden"],
+                   "heads": sz["heads"], "kv_heads": sz["kv_heads"], "head_dim": sz["head_dim"], "intermediate": sz["intermediate"],
+                   "vocab": sz["vocab"], "tied_head": sz["tied"], "global_batch": args.batch, "seq_len": context,
+                   "parallelism": "single-gpu", "l2": f"step reads {weight_bytes / 1e9:.1f} GB of weights, larger than L2",
                    "peaks": which},
         "e2e": {"value": round(args.batch / (e2e["ms"] * 1e-3), 1), "unit": "tok/s",
                 "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])},
