@@ -79,6 +79,13 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // kernel after it may begin its own prologue; the kernels here do so after their own wait, so at
 // most two kernels overlap.  Both calls are no-ops for ordinary launches.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+// The same wait taken by one thread for its CTA: the others park at the CTA barrier instead of
+// each waiting on the grid dependency, which leaves the issue slots of the SM to the kernel that is
+// still running beside them.  Every thread of the CTA must call it.
+__device__ __forceinline__ void pdl_wait_cta() {
+    if (threadIdx.x == 0) pdl_wait();
+    __syncthreads();
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
 // Launch `kernel` so that it may overlap the tail of its predecessor (see pdl_wait).

@@ -51,15 +51,18 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
     // it, let the kernel after this one start its own prologue, and only then read activations.
     int k = k_begin;
     constexpr int PRE = 4;
-    if (k + PRE * 32 <= k_full) {
-        uint4 a_lo[PRE], a_hi[PRE];
+    const bool pre = k + PRE * 32 <= k_full;
+    uint4 a_lo[PRE], a_hi[PRE];
+    if (pre) {
 #pragma unroll
         for (int u = 0; u < PRE; u++) {
             a_lo[u] = ld_stream16(w_lo + k + u * 32);
             a_hi[u] = ld_stream16(w_hi + k + u * 32);
         }
-        pdl_wait();
-        pdl_trigger();
+    }
+    pdl_wait_cta();
+    pdl_trigger();
+    if (pre) {
 #pragma unroll
         for (int u = 0; u < PRE; u++) {
 #pragma unroll
@@ -70,9 +73,6 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
             }
         }
         k += PRE * 32;
-    } else {
-        pdl_wait();
-        pdl_trigger();
     }
 #pragma unroll 4
     for (; k < k_full; k += 32) {
