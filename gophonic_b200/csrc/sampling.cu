@@ -189,30 +189,76 @@ struct SampleParams {
     const int* top_k;
     const float* top_p;
     const uint64_t* seed;
-    const uint64_t* draw;
+    uint64_t* draw;
     int* out;
+    const int* opt_row;  // option index of logits row i (null: i itself)
+    int advance;         // add one to draw[] of every sampled row
 };
 
-__global__ void __launch_bounds__(ST) sample_kernel(SampleParams p) {
+// The walk over the k likeliest candidates, most likely first (cand[i] = key << 32 | ~index, sorted
+// descending): weights, nucleus cut, draw.  Thread 0 does the sums one after another in fp32, the
+// order the reference adds them in.
+__device__ void pick_from_sorted(const SampleParams& p, int r, int o, const float* __restrict__ row, int k, float temp,
+                                 const unsigned long long* cand, float* prob) {
+    const int tid = threadIdx.x;
+    const float inv = 1.f / temp;
+    const int top_i = (int)(0xFFFFFFFFu - (uint32_t)(cand[0] & 0xFFFFFFFFull));
+    const float top = row[top_i];
+    for (int i = tid; i < k; i += ST) {
+        int idx = (int)(0xFFFFFFFFu - (uint32_t)(cand[i] & 0xFFFFFFFFull));
+        prob[i] = expf((row[idx] - top) * inv);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.f;
+        for (int i = 0; i < k; i++) sum += prob[i];
+        int n = k;
+        float tp = p.top_p[o];
+        if (tp > 0.f && tp < 1.f) {
+            float acc = 0.f;
+            for (int i = 0; i < k; i++) {
+                acc += prob[i];
+                if (acc >= tp * sum) {
+                    n = i + 1;
+                    sum = acc;
+                    break;
+                }
+            }
+        }
+        float rr = draw01(p.seed[o], p.draw[o]) * sum;
+        int pick = n - 1;
+        for (int i = 0; i < n; i++) {
+            rr -= prob[i];
+            if (rr <= 0.f) {
+                pick = i;
+                break;
+            }
+        }
+        p.out[r] = (int)(0xFFFFFFFFu - (uint32_t)(cand[pick] & 0xFFFFFFFFull));
+        if (p.advance) p.draw[o] += 1ull;
+    }
+}
+
+// One CTA selects for one row by itself: radix select of the k-th largest logit over the whole row,
+// gather, sort.  `cand` holds at least MAXK entries, `prob` MAXK.
+__device__ void sample_row_full(const SampleParams& p, int r, int o, unsigned long long* cand, float* prob) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ uint32_t bins[256];
     __shared__ uint32_t part[ST / 32];
     __shared__ uint32_t chosen[2];
     __shared__ uint32_t n_gt;
-    __shared__ unsigned long long cand[MAXK];
-    __shared__ float prob[MAXK];
 
-    const int r = blockIdx.x, tid = threadIdx.x;
+    const int tid = threadIdx.x;
     const float* row = p.logits + (int64_t)r * p.stride;
     const int V = p.vocab;
-    const float temp = p.temperature[r];
+    const float temp = p.temperature[o];
     if (!(temp > 0.f)) {
         int t = block_argmax(row, V, s_val, s_idx);
         if (tid == 0) p.out[r] = t;
         return;
     }
-    int k = p.top_k[r];
+    int k = p.top_k[o];
     if (k <= 0 || k > MAXK) k = MAXK;
     if (k > V) k = V;
 
@@ -283,50 +329,152 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleParams p) {
             __syncthreads();
         }
     }
-    // weights, most likely first
-    const float inv = 1.f / temp;
-    const int top_i = (int)(0xFFFFFFFFu - (uint32_t)(cand[0] & 0xFFFFFFFFull));
-    const float top = row[top_i];
-    if (tid < k) {
-        int idx = (int)(0xFFFFFFFFu - (uint32_t)(cand[tid] & 0xFFFFFFFFull));
-        prob[tid] = expf((row[idx] - top) * inv);
+    pick_from_sorted(p, r, o, row, k, temp, cand, prob);
+}
+
+__global__ void __launch_bounds__(ST) sample_kernel(SampleParams p) {
+    __shared__ unsigned long long cand[MAXK];
+    __shared__ float prob[MAXK];
+    const int r = blockIdx.x;
+    sample_row_full(p, r, p.opt_row ? p.opt_row[r] : r, cand, prob);
+}
+
+// ---- wide rows: three kernels ------------------------------------------------------------
+// A row of a large vocabulary is too long for one CTA to scan five times.  (1) CTAs over chunks of
+// the row count the logits by the top 12 bits of their order key into a histogram of the row.
+// (2) Every CTA finds, from the histogram, the lowest bin that the k likeliest logits reach, and
+// appends the logits of its chunk in that bin or above to the row's candidate list.  (3) One CTA
+// per row sorts the candidates (k and the rest of the last bin: a few hundred to a few thousand)
+// by (logit descending, index ascending) and walks them as above.  If the last bin is so crowded
+// that the list overflows (many equal logits), that CTA selects over the whole row by itself.
+// Greedy rows take the same path with k = 1.
+constexpr int HB = 4096;        // histogram bins
+constexpr int WCHUNK = 8192;    // logits per CTA in (1) and (2)
+constexpr int MAXC = 4096;      // candidates kept per row
+constexpr int HROW = HB + 2;    // per row: bins, then the candidate count
+
+__device__ __forceinline__ int row_k(const SampleParams& p, int o) {
+    if (!(p.temperature[o] > 0.f)) return 1;
+    int k = p.top_k[o];
+    if (k <= 0 || k > MAXK) k = MAXK;
+    if (k > p.vocab) k = p.vocab;
+    return k;
+}
+
+__global__ void __launch_bounds__(256) sample_hist_kernel(SampleParams p, uint32_t* __restrict__ hist) {
+    __shared__ uint32_t sh[HB];
+    const int r = blockIdx.y, tid = threadIdx.x;
+    for (int i = tid; i < HB; i += 256) sh[i] = 0;
+    __syncthreads();
+    const float* row = p.logits + (int64_t)r * p.stride;
+    const int lo = blockIdx.x * WCHUNK, hi = lo + WCHUNK < p.vocab ? lo + WCHUNK : p.vocab;
+    for (int i = lo + tid; i < hi; i += 256) atomicAdd(&sh[order_key(row[i]) >> 20], 1u);
+    __syncthreads();
+    uint32_t* h = hist + (int64_t)r * HROW;
+    for (int i = tid; i < HB; i += 256)
+        if (sh[i]) atomicAdd(&h[i], sh[i]);
+}
+
+__global__ void __launch_bounds__(256) sample_gather_kernel(SampleParams p, uint32_t* __restrict__ hist,
+                                                            unsigned long long* __restrict__ cands) {
+    __shared__ uint32_t sh[HB];
+    __shared__ uint32_t seg[256];
+    __shared__ int s_bin;
+    const int r = blockIdx.y, tid = threadIdx.x;
+    const int o = p.opt_row ? p.opt_row[r] : r;
+    uint32_t* h = hist + (int64_t)r * HROW;
+    uint32_t local = 0;
+    for (int i = 0; i < HB / 256; i++) {
+        uint32_t v = h[tid * (HB / 256) + i];
+        sh[tid * (HB / 256) + i] = v;
+        local += v;
     }
+    seg[tid] = local;
     __syncthreads();
     if (tid == 0) {
-        float sum = 0.f;
-        for (int i = 0; i < k; i++) sum += prob[i];
-        int n = k;
-        float tp = p.top_p[r];
-        if (tp > 0.f && tp < 1.f) {
-            float acc = 0.f;
-            for (int i = 0; i < k; i++) {
-                acc += prob[i];
-                if (acc >= tp * sum) {
-                    n = i + 1;
-                    sum = acc;
-                    break;
+        const uint32_t k = (uint32_t)row_k(p, o);
+        uint32_t cum = 0;
+        int bin = 0;
+        for (int t = 255; t >= 0; t--) {
+            if (cum + seg[t] >= k) {
+                for (int b = t * (HB / 256) + HB / 256 - 1; b >= t * (HB / 256); b--) {
+                    cum += sh[b];
+                    if (cum >= k) {
+                        bin = b;
+                        break;
+                    }
                 }
-            }
-        }
-        float rr = draw01(p.seed[r], p.draw[r]) * sum;
-        int pick = n - 1;
-        for (int i = 0; i < n; i++) {
-            rr -= prob[i];
-            if (rr <= 0.f) {
-                pick = i;
                 break;
             }
+            cum += seg[t];
         }
-        p.out[r] = (int)(0xFFFFFFFFu - (uint32_t)(cand[pick] & 0xFFFFFFFFull));
+        s_bin = bin;
     }
+    __syncthreads();
+    const uint32_t bin = (uint32_t)s_bin;
+    const float* row = p.logits + (int64_t)r * p.stride;
+    unsigned long long* c = cands + (int64_t)r * MAXC;
+    const int lo = blockIdx.x * WCHUNK, hi = lo + WCHUNK < p.vocab ? lo + WCHUNK : p.vocab;
+    for (int i = lo + tid; i < hi; i += 256) {
+        const uint32_t key = order_key(row[i]);
+        if ((key >> 20) >= bin) {
+            const uint32_t slot = atomicAdd(&h[HB], 1u);
+            if (slot < (uint32_t)MAXC) c[slot] = ((unsigned long long)key << 32) | (uint32_t)(0xFFFFFFFFu - (uint32_t)i);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(ST) sample_final_kernel(SampleParams p, const uint32_t* __restrict__ hist,
+                                                          const unsigned long long* __restrict__ cands) {
+    __shared__ unsigned long long cand[MAXC];
+    __shared__ float prob[MAXK];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const int o = p.opt_row ? p.opt_row[r] : r;
+    const uint32_t count = hist[(int64_t)r * HROW + HB];
+    if (count > (uint32_t)MAXC) {
+        sample_row_full(p, r, o, cand, prob);
+        return;
+    }
+    const int n = (int)count;
+    int P = 1024;
+    while (P < n) P <<= 1;
+    const unsigned long long* c = cands + (int64_t)r * MAXC;
+    for (int i = tid; i < P; i += ST) cand[i] = i < n ? c[i] : 0ull;
+    __syncthreads();
+    // bitonic sort, descending (empty slots are 0 and sink)
+    for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = tid; t < P / 2; t += ST) {
+                const int i = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
+                const int j = i | stride;
+                unsigned long long a = cand[i], b = cand[j];
+                const bool desc = (i & size) == 0;
+                if (desc ? (a < b) : (a > b)) {
+                    cand[i] = b;
+                    cand[j] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    const float* row = p.logits + (int64_t)r * p.stride;
+    const float temp = p.temperature[o];
+    if (!(temp > 0.f)) {
+        if (tid == 0) p.out[r] = n > 0 ? (int)(0xFFFFFFFFu - (uint32_t)(cand[0] & 0xFFFFFFFFull)) : 0;
+        return;
+    }
+    int k = row_k(p, o);
+    if (k > n) k = n;
+    pick_from_sorted(p, r, o, row, k, temp, cand, prob);
 }
 
 // logits[r, v] -= presence[r] for every token v the reply of row r already holds
 // (qwen3/chat.go:430-437); `seen` is one bit per (row slot, token).
 __global__ void presence_kernel(float* __restrict__ logits, int64_t stride, int vocab, const uint32_t* __restrict__ seen,
-                                int64_t seen_stride, const int* __restrict__ seen_row, const float* __restrict__ presence) {
+                                int64_t seen_stride, const int* __restrict__ seen_row, const float* __restrict__ presence,
+                                int indexed) {
     int r = blockIdx.y;
-    float pen = presence[r];
+    float pen = presence[indexed ? seen_row[r] : r];
     if (pen == 0.f) return;
     int w = blockIdx.x * blockDim.x + threadIdx.x;
     int words = (vocab + 31) / 32;
@@ -375,22 +523,47 @@ GB_API int gb_argmax_wide(const float* logits, int rows, int vocab, int64_t stri
     return 0;
 }
 
-GB_API int gb_sample(const float* logits, int rows, int vocab, int64_t stride, const float* temperature, const int* top_k,
-                     const float* top_p, const uint64_t* seed, const uint64_t* draw, int* out, cudaStream_t stream) {
+// Bytes of scratch gb_sample wants for `rows` rows of `vocab` logits (0: none).
+GB_API int64_t gb_sample_scratch_bytes(int rows, int vocab) {
+    if (vocab < 2 * WCHUNK || rows <= 0) return 0;
+    return (int64_t)rows * (HROW * (int64_t)sizeof(uint32_t) + MAXC * (int64_t)sizeof(unsigned long long));
+}
+
+// One token per row.  opt_row (may be null): which entry of the option arrays row i uses.
+// advance != 0: draw[] of every sampled row is increased by one after the draw.
+GB_API int gb_sample(const float* logits, int rows, int vocab, int64_t stride, const int* opt_row, const float* temperature,
+                     const int* top_k, const float* top_p, const uint64_t* seed, uint64_t* draw, int* out, int advance, void* scratch,
+                     int64_t scratch_bytes, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || stride < vocab) GB_REFUSE("sample: vocab %d, stride %lld", vocab, (long long)stride);
-    SampleParams p{logits, stride, rows, vocab, temperature, top_k, top_p, seed, draw, out};
-    sample_kernel<<<rows, ST, 0, stream>>>(p);
-    GB_CHECK_LAUNCH("sample");
+    SampleParams p{logits, stride, rows, vocab, temperature, top_k, top_p, seed, draw, out, opt_row, advance};
+    const int64_t want = gb_sample_scratch_bytes(rows, vocab);
+    if (want == 0 || !scratch || scratch_bytes < want || rows > 65535) {
+        sample_kernel<<<rows, ST, 0, stream>>>(p);
+        GB_CHECK_LAUNCH("sample");
+        return 0;
+    }
+    if ((uintptr_t)scratch & 7) GB_REFUSE("sample: scratch must be 8-byte aligned");
+    unsigned long long* cands = (unsigned long long*)scratch;
+    uint32_t* hist = (uint32_t*)(cands + (int64_t)rows * MAXC);
+    if (cudaMemsetAsync(hist, 0, (size_t)rows * HROW * sizeof(uint32_t), stream) != cudaSuccess) GB_REFUSE("sample: cannot clear the histograms");
+    const dim3 grid(ceil_div(vocab, WCHUNK), rows);
+    sample_hist_kernel<<<grid, 256, 0, stream>>>(p, hist);
+    GB_CHECK_LAUNCH("sample_hist");
+    sample_gather_kernel<<<grid, 256, 0, stream>>>(p, hist, cands);
+    GB_CHECK_LAUNCH("sample_gather");
+    sample_final_kernel<<<rows, ST, 0, stream>>>(p, hist, cands);
+    GB_CHECK_LAUNCH("sample_final");
     return 0;
 }
 
+// presence[r] belongs to logits row r, or, with indexed != 0, to the bitmap row seen_row[r]
 GB_API int gb_presence_penalty(float* logits, int rows, int vocab, int64_t stride, const uint32_t* seen, int64_t seen_stride,
-                               const int* seen_row, const float* presence, cudaStream_t stream) {
+                               const int* seen_row, const float* presence, int indexed, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (rows > 65535) GB_REFUSE("presence_penalty: %d rows exceed one launch", rows);
     int words = (vocab + 31) / 32;
-    presence_kernel<<<dim3(ceil_div(words, 256), rows), 256, 0, stream>>>(logits, stride, vocab, seen, seen_stride, seen_row, presence);
+    presence_kernel<<<dim3(ceil_div(words, 256), rows), 256, 0, stream>>>(logits, stride, vocab, seen, seen_stride, seen_row, presence, indexed);
     GB_CHECK_LAUNCH("presence_penalty");
     return 0;
 }

@@ -421,10 +421,20 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _check(_lib.gb_argmax(_ptr(logits), c_int(rows), c_int(vocab), c_int64(logits.stride(0)), _ptr(out), _stream()))
 
 
+def sample_scratch_bytes(rows: int, vocab: int) -> int:
+    """Bytes of scratch with which ``sample`` spreads a row of a wide vocabulary over many CTAs."""
+    _lib.gb_sample_scratch_bytes.restype = c_int64
+    return int(_lib.gb_sample_scratch_bytes(c_int(rows), c_int(vocab)))
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           seed: torch.Tensor, draw: torch.Tensor, out: torch.Tensor) -> None:
+           seed: torch.Tensor, draw: torch.Tensor, out: torch.Tensor, opt_row: Optional[torch.Tensor] = None,
+           advance: bool = False, scratch: Optional[torch.Tensor] = None) -> None:
     """One token per row: greedy where temperature <= 0, else top-k / top-p sampling with the
-    counter-based draw (seed[r], draw[r])."""
+    counter-based draw (seed, draw).  Row i takes its options from entry ``opt_row[i]`` of the
+    option tensors (entry i without ``opt_row``); with ``advance`` the kernel adds one to the draw
+    counter of every row it sampled.  ``scratch`` (uint8, ``sample_scratch_bytes``) lets rows of a
+    wide vocabulary be selected by many CTAs; without it one CTA scans each row."""
     _need(logits, "logits", torch.float32, 2, contiguous=False)
     rows = logits.shape[0]
     _need(temperature, "temperature", torch.float32, 1)
@@ -433,16 +443,33 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _need(seed, "seed", torch.int64, 1)
     _need(draw, "draw", torch.int64, 1)
     _need(out, "sample out", torch.int32, 1)
-    for t in (temperature, top_k, top_p, seed, draw, out):
-        if t.numel() < rows:
-            raise KernelError("sample: a per-row option tensor is shorter than the batch")
+    if out.numel() < rows:
+        raise KernelError("sample: out is shorter than the batch")
+    if opt_row is not None:
+        _need(opt_row, "option rows", torch.int32, 1)
+        if opt_row.numel() < rows:
+            raise KernelError("sample: opt_row is shorter than the batch")
+    else:
+        for t in (temperature, top_k, top_p, seed, draw):
+            if t.numel() < rows:
+                raise KernelError("sample: a per-row option tensor is shorter than the batch")
     if logits.stride(1) != 1:
         raise KernelError("sample: logits rows are not contiguous")
-    _check(_lib.gb_sample(_ptr(logits), c_int(rows), c_int(logits.shape[1]), c_int64(logits.stride(0)),
-                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _ptr(out), _stream()))
+    nbytes = 0
+    if scratch is not None:
+        _need(scratch, "sample scratch", torch.uint8, 1)
+        nbytes = scratch.numel()
+    want = sample_scratch_bytes(rows, logits.shape[1])
+    wide = 0 < want <= nbytes
+    _check(_lib.gb_sample(_ptr(logits), c_int(rows), c_int(logits.shape[1]), c_int64(logits.stride(0)), _ptr(opt_row),
+                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _ptr(out),
+                          c_int(1 if advance else 0), _ptr(scratch), c_int64(nbytes), _stream()), 3 if wide else 1)
 
 
-def presence_penalty(logits: torch.Tensor, seen: torch.Tensor, seen_row: torch.Tensor, presence: torch.Tensor) -> None:
+def presence_penalty(logits: torch.Tensor, seen: torch.Tensor, seen_row: torch.Tensor, presence: torch.Tensor,
+                     indexed: bool = False) -> None:
+    """logits[r, v] -= presence for every token v set in bitmap row seen_row[r]; the penalty is
+    presence[r], or presence[seen_row[r]] with ``indexed``."""
     _need(logits, "logits", torch.float32, 2, contiguous=False)
     _need(seen, "seen bitmap", torch.int32, 2)
     _need(seen_row, "seen row", torch.int32, 1)
@@ -451,7 +478,7 @@ def presence_penalty(logits: torch.Tensor, seen: torch.Tensor, seen_row: torch.T
     if seen.shape[1] * 32 < vocab:
         raise KernelError("presence_penalty: bitmap is narrower than the vocabulary")
     _check(_lib.gb_presence_penalty(_ptr(logits), c_int(rows), c_int(vocab), c_int64(logits.stride(0)), _ptr(seen),
-                                    c_int64(seen.stride(0)), _ptr(seen_row), _ptr(presence), _stream()))
+                                    c_int64(seen.stride(0)), _ptr(seen_row), _ptr(presence), c_int(1 if indexed else 0), _stream()))
 
 
 def mark_seen(tokens: torch.Tensor, vocab: int, seen: torch.Tensor, seen_row: torch.Tensor) -> None:

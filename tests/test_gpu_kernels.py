@@ -408,11 +408,16 @@ def test_argmax_first_maximum_nan_and_ties(ops):
     assert out.tolist() == ref
 
 
-@pytest.mark.parametrize("V", [23, 1000, 151936])
-def test_sampler_matches_the_plain_sampler(ops, V):
+@pytest.mark.parametrize("V,wide", [(23, False), (1000, False), (151936, False), (151936, True), (20000, True)])
+def test_sampler_matches_the_plain_sampler(ops, V, wide):
+    """``wide``: with scratch, rows of a wide vocabulary are selected by many CTAs (histogram,
+    gather, sort); without, one CTA scans each row.  Both follow the plain sampler."""
     rows = 12
     logits = rnd(rows, V, scale=2.0, seed=V)
     logits[3, : min(V, 40)] = 1.5           # many ties at the threshold
+    logits[6, 100:6000] = 9.0               # thousands of equal logits on top: the candidate list overflows
+    scratch = torch.zeros(ops.sample_scratch_bytes(rows, V), dtype=torch.uint8, device=DEV) if wide else None
+    assert (scratch is None) or scratch.numel() > 0
     temps = [0.8, 1.0, 0.0, 0.7, 1.3, 0.5, 1.0, 1.0, 2.0, 0.9, 1.0, 0.3]
     ks = [20, 0, 5, 10, 1, 2000, 50, 3, 0, 7, 1024, 2]
     ps = [0.0, 0.9, 0.5, 0.0, 0.0, 0.95, 1.0, 0.5, 0.2, 0.0, 0.99, 0.0]
@@ -421,8 +426,11 @@ def test_sampler_matches_the_plain_sampler(ops, V):
         draws = [draw0 + i for i in range(rows)]
         mk = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
         out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        draws_dev = mk(draws, torch.int64)
         ops.sample(logits, mk(temps, torch.float32), mk(ks, torch.int32), mk(ps, torch.float32),
-                   mk(seeds, torch.int64), mk(draws, torch.int64), out)
+                   mk(seeds, torch.int64), draws_dev, out, scratch=scratch, advance=wide)
+        if wide:  # the kernel advanced the counters of the rows it sampled, not of the greedy one
+            assert draws_dev.tolist() == [d + (1 if temps[i] > 0 else 0) for i, d in enumerate(draws)]
         host = logits.cpu().numpy()
         for r in range(rows):
             tok, cand, probs = P.sample_token(host[r], temps[r], ks[r], ps[r], seeds[r], draws[r])
@@ -454,6 +462,23 @@ def test_sampler_distribution_and_batch_independence(ops):
         ops.sample(logits[:1], mk([1.0], torch.float32), mk([3], torch.int32), mk([0.0], torch.float32),
                    mk([42], torch.int64), mk([i], torch.int64), one)
         assert one.item() == out[i].item()
+
+
+def test_sampler_rows_take_their_options_by_index(ops):
+    """opt_row: logits row i uses entry opt_row[i] of the option tables, as a batch whose shorter
+    requests have ended does."""
+    V = 40000
+    logits = rnd(3, V, scale=2.0, seed=3)
+    mk = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
+    temps, ks, ps = mk([0.0, 0.9, 0.0, 0.0, 0.7, 1.1], torch.float32), mk([0, 30, 0, 0, 0, 5], torch.int32), mk([0, 0.9, 0, 0, 0.5, 0], torch.float32)
+    seeds, draws = mk([0, 11, 0, 0, 12, 13], torch.int64), mk([0, 4, 0, 0, 9, 2], torch.int64)
+    opt_row = mk([5, 1, 4], torch.int32)
+    out, ref = torch.empty(3, dtype=torch.int32, device=DEV), torch.empty(3, dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(ops.sample_scratch_bytes(3, V), dtype=torch.uint8, device=DEV)
+    ops.sample(logits, temps, ks, ps, seeds, draws.clone(), out, opt_row=opt_row, scratch=scratch)
+    pick = opt_row.long()
+    ops.sample(logits, temps[pick], ks[pick], ps[pick], seeds[pick], draws[pick], ref)
+    assert out.tolist() == ref.tolist()
 
 
 def test_presence_penalty_and_seen_bitmap(ops):
