@@ -203,26 +203,47 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
 }
 
 // out[seq, head, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over the key splits.
+// One CTA of 128 threads per (sequence, head).  The first warp reads every split's maximum and sum
+// at once and leaves the weights exp(m_s - M) in shared memory (maximum and normaliser by shuffle
+// trees, a fixed order); then thread c adds column c of the splits in split order.
+constexpr int MERGE_MAX_SPLITS = 256;
+
 template <typename T>
-__global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t out_row_stride,
-                                  const int* __restrict__ seq_q_start, int heads, int d, int num_splits) {
-    pdl_wait();
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t out_row_stride,
+                                                         const int* __restrict__ seq_q_start, int heads, int d, int num_splits) {
+    __shared__ float w_s[MERGE_MAX_SPLITS];
+    __shared__ float l_s;
     pdl_trigger();  // the product that follows may start fetching its weights
-    int head = blockIdx.x, seq = blockIdx.y;
+    const int head = blockIdx.x, seq = blockIdx.y;
     const float* sp = scratch + ((int64_t)seq * heads + head) * num_splits * (d + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < num_splits; s++) M = fmaxf(M, sp[(int64_t)s * (d + 2)]);
-    float L = 0.f;
-    for (int s = 0; s < num_splits; s++) {
-        float ms = sp[(int64_t)s * (d + 2)];
-        if (ms != -INFINITY) L += expf(ms - M) * sp[(int64_t)s * (d + 2) + 1];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float M = -INFINITY;
+        for (int s = lane; s < num_splits; s += 32) M = fmaxf(M, sp[(int64_t)s * (d + 2)]);
+        M = warp_max(M);
+        float L = 0.f;
+        for (int s = lane; s < num_splits; s += 32) {
+            const float ms = sp[(int64_t)s * (d + 2)];
+            const float w = ms != -INFINITY ? expf(ms - M) : 0.f;
+            w_s[s] = w;
+            L += w * sp[(int64_t)s * (d + 2) + 1];
+        }
+        L = warp_sum(L);
+        if (lane == 0) l_s = L;
     }
+    __syncthreads();
+    const float L = l_s;
     T* op = out + (int64_t)seq_q_start[seq] * out_row_stride + (int64_t)head * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < num_splits; s++) {
-            float ms = sp[(int64_t)s * (d + 2)];
-            if (ms != -INFINITY) a += expf(ms - M) * sp[(int64_t)s * (d + 2) + 2 + c];
+        // sixteen loads in flight at a time; the sum itself stays in split order
+        for (int s0 = 0; s0 < num_splits; s0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) v[j] = s0 + j < num_splits ? sp[(int64_t)(s0 + j) * (d + 2) + 2 + c] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (s0 + j < num_splits) a += w_s[s0 + j] * v[j];
         }
         op[c] = from_f32<T>(a / L);
     }
@@ -278,6 +299,7 @@ int launch(const AttnParams& p, cudaStream_t stream) {
 // Merge of per-split partial results, shared with the tensor-core single-token kernel.
 int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
                               int nseq, int heads, int d, int num_splits, cudaStream_t stream) {
+    if (num_splits > MERGE_MAX_SPLITS) GB_REFUSE("attention: %d key splits; at most %d", num_splits, MERGE_MAX_SPLITS);
     if (dtype == GB_F32)
         attn_merge_kernel<float><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (float*)out, out_row_stride, seq_q_start, heads, d, num_splits);
     else
@@ -292,7 +314,7 @@ GB_API int gb_attention_simt(const AttnParams* pp, int dtype, cudaStream_t strea
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("attention: %d heads over %d kv heads", p.heads, p.kv_heads);
     if (p.d <= 0 || p.d > 256) GB_REFUSE("attention_simt: head_dim %d is outside [1, 256]", p.d);
-    if (p.num_splits < 1) GB_REFUSE("attention: %d key splits", p.num_splits);
+    if (p.num_splits < 1 || p.num_splits > MERGE_MAX_SPLITS) GB_REFUSE("attention: %d key splits; 1 to %d", p.num_splits, MERGE_MAX_SPLITS);
     if (p.num_splits > 1 && p.max_q_len != 1) GB_REFUSE("attention: key splits need single-token rows, got rows of up to %d", p.max_q_len);
     if (p.num_splits > 1 && !p.scratch) GB_REFUSE("attention: %d key splits without scratch memory", p.num_splits);
     if (p.window < 0) GB_REFUSE("attention: window %d", p.window);

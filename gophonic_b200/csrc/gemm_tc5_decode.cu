@@ -242,16 +242,36 @@ int dispatch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t
 
 }  // namespace
 
-// How many slices of K the kernel would like for this shape on a device with `sms` SMs (two CTAs
-// fit an SM): a power of two that keeps at most about 2 * sms CTAs, at least eight K steps of 64 a
-// slice, at most 8.
-GB_API int gb_gemm_tc5_decode_splits(int N, int K, int sms) {
-    int tiles = ceil_div(N, BMW), KB = ceil_div(K, BK);
-    int want = (2 * sms) / (tiles > 0 ? tiles : 1);
-    if (want > KB / 8) want = KB / 8;
-    int s = 1;
-    while (s * 2 <= want && s < 8) s *= 2;  // a cluster of 1, 2, 4 or 8 CTAs
-    return s;
+// How many slices of K (1, 2, 4 or 8, the size of the cluster) the kernel would like for M rows of
+// this shape on a device with `sms` SMs, two CTAs to an SM.
+//   More than 16 rows: the most slices that keep at most about 2 * sms CTAs and at least eight K
+//   steps of 64 a slice; CTAs that queue behind a full machine cost more than they gain (24576 x 4096
+//   at 64 rows: 40.8 us whole, 57.6 us in two slices).
+//   Up to 16 rows a CTA is lighter and a short queue pays: a CTA's time is its K steps plus about
+//   eight steps of fixed cost, and the choice minimises queue depth x CTA time (24576 x 4096 at 16
+//   rows: 36.5 us in two slices, 38.0 whole, 39.3 in four).
+GB_API int gb_gemm_tc5_decode_splits(int M, int N, int K, int sms) {
+    const int tiles = ceil_div(N, BMW), KB = ceil_div(K, BK);
+    if (sms <= 0) sms = 1;
+    if (M > 16) {
+        int want = (2 * sms) / (tiles > 0 ? tiles : 1);
+        if (want > KB / 8) want = KB / 8;
+        int s = 1;
+        while (s * 2 <= want && s < 8) s *= 2;
+        return s;
+    }
+    int best = 1;
+    double best_cost = 0.0;
+    for (int s = 1; s <= 8; s *= 2) {
+        if (s > 1 && KB / s < 1) break;
+        const double queue = tiles * (double)s / (2.0 * sms);
+        const double cost = (queue > 1.0 ? queue : 1.0) * ((double)ceil_div(KB, s) + 8.0);
+        if (s == 1 || cost < best_cost) {
+            best = s;
+            best_cost = cost;
+        }
+    }
+    return best;
 }
 
 // epi = 0: Y[M, N].  epi = 1: Y[M, N / 2] = silu(gate) * up with gate/up rows of W interleaved in

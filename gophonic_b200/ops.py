@@ -259,7 +259,7 @@ def _tc5_decode(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -
     dev = a.device
     if dev not in _sm_count:
         _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
-    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(N), c_int(K), c_int(_sm_count[dev])))
+    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sm_count[dev])))
     _check(_lib.gb_gemm_tc5_decode(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                    c_int64(a.stride(0)), c_int64(out.stride(0)), c_int(epi), c_int(splits), _stream()))
 
