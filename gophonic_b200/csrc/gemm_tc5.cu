@@ -20,6 +20,8 @@
 // gb_gemm_tc5_status().
 #include "tc5.cuh"
 
+#include <string.h>
+
 __device__ int g_tc5_status;
 
 namespace {
@@ -74,6 +76,29 @@ __device__ __forceinline__ void store_cols32(TC* __restrict__ C, int64_t ldc, in
 #pragma unroll
                 for (int e = 0; e < 16; e++)
                     if (e < left) dst[e] = from_f32<TC>(act[e]);
+            }
+        }
+        return;
+    }
+    if (epi == 2) {
+        // C is the fp32 residual stream: the product is added to it in place
+        if (row < M && sizeof(TC) == 4) {
+            float* dst = reinterpret_cast<float*>(C) + (int64_t)row * ldc + n0c;
+            if ((ldc & 3) == 0 && (((uintptr_t)C & 15) == 0) && n0c + 32 <= N) {
+                float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    float4 v = d4[e];
+                    v.x += __uint_as_float(r[e * 4]);
+                    v.y += __uint_as_float(r[e * 4 + 1]);
+                    v.z += __uint_as_float(r[e * 4 + 2]);
+                    v.w += __uint_as_float(r[e * 4 + 3]);
+                    d4[e] = v;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; e++)
+                    if (n0c + e < N) dst[e] += __uint_as_float(r[e]);
             }
         }
         return;
@@ -267,6 +292,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_kernel(const __grid_constant
 constexpr int PAIR_STAGES = 3, PAIR_BK = 128;  // a stage holds two 64-wide panels of each operand
 constexpr int PAIR_PANEL = 128 * 64 * 2;
 constexpr int PAIR_A_BYTES = 2 * PAIR_PANEL, PAIR_B_BYTES = 2 * PAIR_PANEL, PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_STAGING_BYTES = 4 * 2 * 4096;  // epilogue staging for TMA reductions into C
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // a shared-memory address of either CTA of a pair -> the first CTA's
 
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
@@ -308,10 +334,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 template <typename TC>
 __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                               const __grid_constant__ CUtensorMap map_w, TC* __restrict__ C, int M,
-                                                               int N, int K, int64_t ldc, int epi) {
+                                                               const __grid_constant__ CUtensorMap map_w,
+                                                               const __grid_constant__ CUtensorMap map_c, TC* __restrict__ C, int M, int N,
+                                                               int K, int64_t ldc, int epi) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* staging = tiles + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES;  // [4 epilogue warps][2][32 x 32 floats]
     __shared__ uint64_t full_bar[PAIR_STAGES], empty_bar[PAIR_STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
@@ -444,6 +472,29 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
                 if (n0 + c0 >= N) break;  // uniform across the warp
                 uint32_t r[32];
                 tmem_ld32(t_addr + (uint32_t)c0, r);
+                if (epi == 2) {
+                    // C += tile: the warp lays its 32 x 32 floats out in shared memory (128-byte rows,
+                    // 16-byte pieces swizzled as the tensor map says) and one lane hands them to a TMA
+                    // reduction, which adds them to C in memory; nothing is read back here.  Two
+                    // staging buffers a warp: the reduction issued two chunks ago has read its buffer.
+                    const int sb = (c0 >> 5) & 1;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                    __syncwarp();
+                    unsigned char* stg = staging + (size_t)((quad * 2 + sb) * 4096);
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + ((e ^ (lane & 7)) << 4)) =
+                            make_uint4(r[e * 4], r[e * 4 + 1], r[e * 4 + 2], r[e * 4 + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(&map_c),
+                                     "r"(s32(stg)), "r"(n0 + c0), "r"(m0 + quad * 32)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    }
+                    continue;
+                }
                 store_cols32<TC>(C, ldc, row, M, N, n0 + c0, r, epi, vec_ok);
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -451,6 +502,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
             if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
         }
     }
+    if (epi == 2 && warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // this warp's reductions are done
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     cluster_sync_all();  // neither CTA leaves while the other may still read its memory or signal its barriers
@@ -462,16 +514,30 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
 
 template <typename TC>
 int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, int epi, cudaStream_t stream) {
-    const int smem = PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+    const int smem = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_STAGING_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc5_pair_kernel<TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) GB_REFUSE("gemm_tc5_pair: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    CUtensorMap map_a, map_w;
+    CUtensorMap map_a, map_w, map_c;
     if (int rc = tc5_make_map(&map_a, A, M, K, lda, 128)) return rc;
     if (int rc = tc5_make_map(&map_w, W, N, K, K, 128)) return rc;
+    memset(&map_c, 0, sizeof(map_c));
+    if (epi == 2) {
+        // float32 C in boxes of 32 x 32, 128-byte swizzle, for the epilogue's TMA reductions
+        Tc5EncodeTiledFn fn = tc5_encode_fn();
+        if (!fn) GB_REFUSE("tcgen05 kernels: the driver offers no cuTensorMapEncodeTiled");
+        if ((ldc & 3) || ((uintptr_t)C & 15)) GB_REFUSE("gemm_tc5: adding into C needs 16-byte aligned rows (stride %lld)", (long long)ldc);
+        cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+        cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+        cuuint32_t box[2] = {32u, 32u};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = fn(&map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) GB_REFUSE("gemm_tc5: cuTensorMapEncodeTiled for C failed with code %d", (int)r);
+    }
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -482,7 +548,7 @@ int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int6
     if (total > 0x7fffffff) GB_REFUSE("gemm_tc5_pair: %lld tiles are too many", (long long)total);
     const int pairs = total < sms / 2 ? (int)total : sms / 2;  // one pair of CTAs per pair of SMs walks the tiles
     cudaError_t e = launch_pdl_cluster(gemm_tc5_pair_kernel<TC>, dim3(2 * pairs), dim3(THREADS), (size_t)smem, stream, 2, 1, map_a, map_w,
-                                       (TC*)C, M, N, K, ldc, epi);
+                                       map_c, (TC*)C, M, N, K, ldc, epi);
     if (e != cudaSuccess) GB_REFUSE("gemm_tc5_pair: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -520,7 +586,8 @@ static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N,
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5: K = %d must be a positive multiple of 8", K);
     if ((lda & 7) || lda < K) GB_REFUSE("gemm_tc5: row stride %lld of A must be a multiple of 8 and at least K", (long long)lda);
-    if (epi == 0 && ldc < N) GB_REFUSE("gemm_tc5: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
+    if ((epi == 0 || epi == 2) && ldc < N) GB_REFUSE("gemm_tc5: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
+    if (epi == 2 && c_dtype != GB_F32) GB_REFUSE("gemm_tc5: adding into C needs a float32 C");
     if (epi == 1 && ((N & 15) || ldc < N / 2)) GB_REFUSE("gemm_tc5: the SwiGLU epilogue needs N = %d to be a multiple of 16", N);
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5: operands must be 16-byte aligned");
     if (pair) {
@@ -546,6 +613,11 @@ GB_API int gb_gemm_tc5_pair(const void* A, const void* W, void* C, int c_dtype, 
 GB_API int gb_gemm_tc5_pair_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
                                    cudaStream_t stream) {
     return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, 1, 1, stream);
+}
+
+// C[M, N] += A W^T for a float32 C (the residual stream), on the paired-SM kernel.
+GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream) {
+    return tc5(A, W, C, GB_F32, M, N, K, lda, ldc, 2, 1, stream);
 }
 
 // C[M, N / 2] = silu(A Wg^T) * (A Wu^T); W holds gate and up rows interleaved in blocks of eight.

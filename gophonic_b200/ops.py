@@ -127,6 +127,26 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) 
                           c_int(1 if interleave8 else 0), _stream()))
 
 
+def gemm_add_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether ``gemm_add`` takes this product: a prompt-sized bfloat16 product into a float32 ``out``."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.float32 and a.dim() == 2
+            and a.shape[0] >= TC5_PAIR_MIN_ROWS and _has("gb_gemm_tc5_pair_add") and w.is_contiguous() and tc5_accepts(a, w, out))
+
+
+def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out += a @ w^T in the epilogue of the tiled tcgen05 kernel (``out`` float32: the residual
+    stream); the sum per element is out + product, both float32, as a separate add would give."""
+    _need(a, "gemm a", torch.bfloat16, 2, contiguous=False)
+    _need(w, "gemm w", torch.bfloat16, 2)
+    _need(out, "gemm out", torch.float32, 2, contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or a.stride(1) != 1 or out.stride(1) != 1 or not gemm_add_accepts(a, w, out):
+        raise KernelError(f"gemm_add: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_gemm_tc5_pair_add(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int64(a.stride(0)),
+                                     c_int64(out.stride(0)), _stream()))
+
+
 def gemm_swiglu_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether ``gemm_swiglu`` takes this product: bfloat16, interleaved gate/up rows, and a row
     count one of the kernels with the fused epilogue handles (up to 64, or at least 128)."""

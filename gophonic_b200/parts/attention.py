@@ -66,6 +66,18 @@ class Attention(Mixer):
         self.position.prepare(capacity)
 
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+        self.rt.ops.gemm(self._context(batch, x, cache), self.o, out)
+
+    def adds_in_place(self, rows: int) -> bool:
+        ops = self.rt.ops
+        return (self.o.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.q_dim % 8 == 0
+                and hasattr(ops, "gemm_add") and rows >= ops.TC5_PAIR_MIN_ROWS)
+
+    def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
+        self.rt.ops.gemm_add(self._context(batch, x, cache), self.o, h)
+
+    def _context(self, batch, x: torch.Tensor, cache) -> torch.Tensor:
+        """Everything up to the output projection: [rows, heads * head_dim] in the activation dtype."""
         ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
         if cache is None:
@@ -86,4 +98,4 @@ class Attention(Mixer):
                       batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len, batch.nseq,
                       batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),
                       splits, scratch)
-        ops.gemm(ctx, self.o, out)
+        return ctx

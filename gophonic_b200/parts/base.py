@@ -108,7 +108,18 @@ class Mixer(Part):
     def prepare(self, capacity: int) -> None:
         pass
 
+    def adds_in_place(self, rows: int) -> bool:
+        """True if, for a step of ``rows`` rows, ``forward_into(batch, x, h, cache)`` is the faster
+        way: the part then adds its output to the fp32 residual ``h`` itself (in the epilogue of its
+        last product) and the block has no addend to hand on.  The sum must be the one a separate
+        fp32 add would give.  The default is False: ``forward`` into a buffer of its own."""
+        return False
+
 
 class FeedForward(Part):
-    """forward(batch, x, out): x [rows, hidden] activation dtype -> out [rows, hidden] fp32."""
+    """forward(batch, x, out): x [rows, hidden] activation dtype -> out [rows, hidden] fp32.
+    Optionally ``adds_in_place(rows)`` / ``forward_into(batch, x, h)`` as for a mixer."""
     category = "feed_forward"
+
+    def adds_in_place(self, rows: int) -> bool:
+        return False

@@ -1,8 +1,10 @@
 """Block arrangements: how a layer's mixer, feed-forward and norms are wired around the residual.
 
-``PreNormBlock``: h += mixer(norm_m(h)); h += ffn(norm_f(h)).  The feed-forward's output is not
-added at once: it is handed on as ``delta`` and added by whatever norms the residual next (the
-next block's first norm, or the final norm), in the same kernel that takes the statistics
+``PreNormBlock``: h += mixer(norm_m(h)); h += ffn(norm_f(h)).  A part's output is either added to
+the residual by the part itself, in the epilogue of its last product (prompt-sized steps of the
+built-in parts: ``adds_in_place``), or it is not added at once: it is handed on as ``delta`` and
+added by whatever norms the residual next (the layer's second norm, the next block's first norm,
+or the final norm), in the same kernel that takes the statistics
 (internal/qwen3lm/evaluator.go:641-647, 678-682; ops.go:94-108 does the same).  The residual h
 stays fp32 throughout.
 """
@@ -50,14 +52,21 @@ class PreNormBlock(Part):
 
     def forward(self, batch, h: torch.Tensor, delta: Optional[torch.Tensor], cache) -> torch.Tensor:
         """Runs the layer on residual ``h`` (fp32, updated in place) with the pending addend
-        ``delta``; returns the new pending addend."""
+        ``delta`` (or None); returns the new pending addend (None if everything is added)."""
         rows, hidden = h.shape
         act = self.rt.act_dtype
         x = torch.empty((rows, hidden), dtype=act, device=h.device)
         self.mixer_norm.forward(h, x, delta)
-        mixed = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
-        self.mixer.forward(batch, x, mixed, cache)
+        if self.mixer.adds_in_place(rows):
+            self.mixer.forward_into(batch, x, h, cache)   # h += mixer(x) in the mixer's own last kernel
+            mixed = None
+        else:
+            mixed = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
+            self.mixer.forward(batch, x, mixed, cache)
         self.feed_forward_norm.forward(h, x, mixed)
+        if self.feed_forward.adds_in_place(rows):
+            self.feed_forward.forward_into(batch, x, h)
+            return None
         out = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
         self.feed_forward.forward(batch, x, out)
         return out

@@ -41,6 +41,18 @@ class SwiGLU(FeedForward):
         return self.gate_up.numel() * self.gate_up.element_size() + self.down.numel() * self.down.element_size()
 
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
+        self.rt.ops.gemm(self._activation(x), self.down, out)
+
+    def adds_in_place(self, rows: int) -> bool:
+        ops = self.rt.ops
+        return (self.down.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.spec.intermediate % 8 == 0
+                and hasattr(ops, "gemm_add") and rows >= ops.TC5_PAIR_MIN_ROWS)
+
+    def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor) -> None:
+        self.rt.ops.gemm_add(self._activation(x), self.down, h)
+
+    def _activation(self, x: torch.Tensor) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T): [rows, intermediate] in the activation dtype."""
         ops = self.rt.ops
         rows = x.shape[0]
         act = torch.empty((rows, self.spec.intermediate), dtype=x.dtype, device=x.device)
@@ -50,4 +62,4 @@ class SwiGLU(FeedForward):
             gu = torch.empty((rows, 2 * self.spec.intermediate), dtype=x.dtype, device=x.device)
             ops.gemm(x, self.gate_up, gu)
             ops.swiglu(gu, act, self.interleaved)
-        ops.gemm(act, self.down, out)
+        return act

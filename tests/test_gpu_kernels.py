@@ -158,6 +158,23 @@ def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
     close(out, a.double() @ w.double().T, 2e-5 if out_dtype == torch.float32 else 6e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(192, 96, 64), (300, 1000, 512), (2048, 520, 1032), (257, 96, 4104)])
+def test_gemm_adds_into_the_residual(ops, M, N, K):
+    """out += a w^T in the epilogue: the same bits as the product into a buffer and a float32 add."""
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+    h = rnd(M, N, seed=3)
+    assert ops.gemm_add_accepts(a, w, h)
+    prod = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ops.gemm(a, w, prod, algo="tc5_pair")
+    want = h + prod
+    ops.gemm_add(a, w, h)
+    assert ops.tc5_status() == 0
+    assert torch.equal(h, want)
+    close(h, rnd(M, N, seed=3).double() + a.double() @ w.double().T, 2e-5)
+    small = rnd(8, K, dtype=torch.bfloat16, seed=4)
+    assert not ops.gemm_add_accepts(small, w, torch.empty((8, N), device=DEV))
+
+
 def test_gemm_dispatch_never_puts_float32_on_tensor_cores(ops):
     a, w = rnd(4, 64), rnd(8, 64)
     out = torch.empty((4, 8), device=DEV)
