@@ -364,62 +364,93 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     }
 }
 
-// The common geometry (bfloat16, head_dim 128 rotated in full): a warp per (row, head), every lane
-// holds four consecutive elements, so element i and its partner i + 64 sit in lanes l and l ^ 16.
+// The common geometry (bfloat16, head_dim 128 rotated in full): a warp per head and ROPE_ROWS
+// consecutive rows, every lane holds four consecutive elements of each row, so element i and its
+// partner i + 64 sit in lanes l and l ^ 16.  All loads of the warp's rows (positions, elements,
+// angles, page numbers) are issued before anything is computed: a row is only 256 bytes per head,
+// and it takes several in flight per thread to keep the memory system busy.
+constexpr int ROPE_ROWS = 4;
+
 __global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) {
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x;
+    const int r0 = blockIdx.x * ROPE_ROWS;
     const int head = blockIdx.y * 8 + warp;
     const int total_heads = p.heads + 2 * p.kv_heads;
     if (head >= total_heads) return;
     typedef __nv_bfloat16 bf;
-    bf* src = (bf*)p.qkv + (int64_t)r * p.row_stride + (int64_t)head * 128 + lane * 4;
-    const int pos = p.row_pos[r];
     const bool is_q = head < p.heads;
     const bool is_k = !is_q && head < p.heads + p.kv_heads;
-    bf* dst = src;
-    if (!is_q) {
-        if (!p.write_kv) return;
-        const int kvh = is_k ? head - p.heads : head - p.heads - p.kv_heads;
-        const int slot = p.seq_slot[p.row_seq[r]];
-        const int64_t page = page_of(p.block_table + (int64_t)slot * p.bt_stride, pos, p.ring_pages);
-        bf* plane = (bf*)(is_k ? p.k_plane : p.v_plane);
-        dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)128 + lane * 4;
+    if (!is_q && !p.write_kv) return;
+    const int kvh = is_q ? 0 : (is_k ? head - p.heads : head - p.heads - p.kv_heads);
+    const float* w = is_q ? p.q_w : p.k_w;
+    const int ci = (lane & 15) * 4;  // index into the 64 angles of a position
+
+    int pos[ROPE_ROWS];
+    uint2 raw[ROPE_ROWS];
+    bf* dst[ROPE_ROWS];
+    float4 c[ROPE_ROWS], sn[ROPE_ROWS];
+#pragma unroll
+    for (int j = 0; j < ROPE_ROWS; j++) {
+        const int r = r0 + j < p.rows ? r0 + j : p.rows - 1;  // rows past the end repeat the last one and are not stored
+        pos[j] = p.row_pos[r];
+        bf* src = (bf*)p.qkv + (int64_t)r * p.row_stride + (int64_t)head * 128 + lane * 4;
+        raw[j] = *reinterpret_cast<const uint2*>(src);
+        dst[j] = src;
     }
-    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    if (!is_q) {
+        int slot[ROPE_ROWS];
+#pragma unroll
+        for (int j = 0; j < ROPE_ROWS; j++) {
+            const int r = r0 + j < p.rows ? r0 + j : p.rows - 1;
+            slot[j] = p.seq_slot[p.row_seq[r]];
+        }
+#pragma unroll
+        for (int j = 0; j < ROPE_ROWS; j++) {
+            const int64_t page = page_of(p.block_table + (int64_t)slot[j] * p.bt_stride, pos[j], p.ring_pages);
+            bf* plane = (bf*)(is_k ? p.k_plane : p.v_plane);
+            dst[j] = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos[j] % GB_PAGE)) * (int64_t)128 + lane * 4;
+        }
+    }
     if (!is_q && !is_k) {
-        *reinterpret_cast<uint2*>(dst) = raw;
+#pragma unroll
+        for (int j = 0; j < ROPE_ROWS; j++)
+            if (r0 + j < p.rows) *reinterpret_cast<uint2*>(dst[j]) = raw[j];
         return;
     }
-    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    float y[4] = {__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi)};
-    const float* w = is_q ? p.q_w : p.k_w;
-    if (w) {
-        float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
-        const float inv = 1.0f / sqrtf(ss / 128.f + p.eps);
-        const float4 ww = *reinterpret_cast<const float4*>(w + lane * 4);
-        y[0] = y[0] * inv * ww.x;
-        y[1] = y[1] * inv * ww.y;
-        y[2] = y[2] * inv * ww.z;
-        y[3] = y[3] * inv * ww.w;
-    }
-    const int ci = (lane & 15) * 4;  // index into the 64 angles of this position
-    const float4 c = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)pos * 64 + ci);
-    const float4 s = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)pos * 64 + ci);
-    const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
-    float o[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const float partner = __shfl_xor_sync(0xffffffffu, y[j], 16);
-        o[j] = lane < 16 ? y[j] * cs[j] - partner * sn[j] : y[j] * cs[j] + partner * sn[j];
+    for (int j = 0; j < ROPE_ROWS; j++) {
+        c[j] = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)pos[j] * 64 + ci);
+        sn[j] = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)pos[j] * 64 + ci);
     }
-    const __nv_bfloat162 o0 = __floats2bfloat162_rn(o[0], o[1]), o1 = __floats2bfloat162_rn(o[2], o[3]);
-    uint2 out;
-    out.x = *reinterpret_cast<const uint32_t*>(&o0);
-    out.y = *reinterpret_cast<const uint32_t*>(&o1);
-    *reinterpret_cast<uint2*>(dst) = out;
+    float4 ww = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (w) ww = *reinterpret_cast<const float4*>(w + lane * 4);
+#pragma unroll
+    for (int j = 0; j < ROPE_ROWS; j++) {
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw[j].x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw[j].y);
+        float y[4] = {__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi)};
+        if (w) {
+            float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+            const float inv = 1.0f / sqrtf(ss / 128.f + p.eps);
+            y[0] = y[0] * inv * ww.x;
+            y[1] = y[1] * inv * ww.y;
+            y[2] = y[2] * inv * ww.z;
+            y[3] = y[3] * inv * ww.w;
+        }
+        const float cs[4] = {c[j].x, c[j].y, c[j].z, c[j].w}, sv[4] = {sn[j].x, sn[j].y, sn[j].z, sn[j].w};
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float partner = __shfl_xor_sync(0xffffffffu, y[e], 16);
+            o[e] = lane < 16 ? y[e] * cs[e] - partner * sv[e] : y[e] * cs[e] + partner * sv[e];
+        }
+        const __nv_bfloat162 o0 = __floats2bfloat162_rn(o[0], o[1]), o1 = __floats2bfloat162_rn(o[2], o[3]);
+        uint2 out;
+        out.x = *reinterpret_cast<const uint32_t*>(&o0);
+        out.y = *reinterpret_cast<const uint32_t*>(&o1);
+        if (r0 + j < p.rows) *reinterpret_cast<uint2*>(dst[j]) = out;
+    }
 }
 
 GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStream_t stream) {
@@ -434,7 +465,7 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     if (dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
         !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
         ceil_div(total_heads, 8) <= 65535) {
-        launch_pdl(qk_rope_bf16_d128_kernel, dim3(p.rows, ceil_div(total_heads, 8)), dim3(256), 0, stream, p);
+        launch_pdl(qk_rope_bf16_d128_kernel, dim3(ceil_div(p.rows, ROPE_ROWS), ceil_div(total_heads, 8)), dim3(256), 0, stream, p);
         GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
         return 0;
     }
