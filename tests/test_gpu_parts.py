@@ -344,3 +344,211 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype)
         for i in range(3):
             assert rel(np.concatenate(got[i], 0), refs[i]) < tol, (round_, i)
             eng.end_sequence(slots[i])
+
+
+# ---- a toy feed-forward with routing and a toy position encoding ----------------------------------
+# Both are defined here, registered through the registry and used beside the built-in parts, layer
+# by layer, without a change to the package.
+@dataclass(frozen=True)
+class Top1Spec:
+    hidden: int
+    experts: int
+    inner: int
+    kind: str = "toy-top1"
+
+
+@dataclass(frozen=True)
+class SlowRotarySpec:
+    """Rotary angles of position / slowdown: another position encoding for the built-in attention."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    slowdown: float
+    kind: str = "toy-slow-rope"
+
+
+def _routed_ffn():
+    from gophonic_b200.parts.base import FeedForward, TensorDecl
+
+    class Top1Experts(FeedForward):
+        """Router logits in fp32, the single best expert per row (lowest index on ties), output =
+        softmax weight of that expert times relu(x W1_e^T) W2_e^T.  Rows are grouped by expert
+        inside forward."""
+
+        @classmethod
+        def declare(cls, spec, prefix):
+            d = [TensorDecl(prefix + "router.weight", (spec.experts, spec.hidden))]
+            for e in range(spec.experts):
+                d += [TensorDecl(prefix + f"experts.{e}.w1.weight", (spec.inner, spec.hidden)),
+                      TensorDecl(prefix + f"experts.{e}.w2.weight", (spec.hidden, spec.inner))]
+            return d
+
+        def __init__(self, spec, prefix, tensors, runtime):
+            self.spec = spec
+            self.router = tensors[prefix + "router.weight"].float()
+            self.w1 = [tensors[prefix + f"experts.{e}.w1.weight"].float() for e in range(spec.experts)]
+            self.w2 = [tensors[prefix + f"experts.{e}.w2.weight"].float() for e in range(spec.experts)]
+
+        def forward(self, batch, x, out):
+            xf = x.float()
+            logits = xf @ self.router.T
+            prob = torch.softmax(logits, dim=-1)
+            best = torch.argmax(logits, dim=-1)
+            out.zero_()
+            for e in range(self.spec.experts):
+                rows = torch.nonzero(best == e).flatten()
+                if rows.numel():
+                    y = torch.relu(xf[rows] @ self.w1[e].T) @ self.w2[e].T
+                    out[rows] = y * prob[rows, e:e + 1]
+    return Top1Experts
+
+
+def _slow_rope():
+    from gophonic_b200.parts.base import PositionEncoding
+
+    class SlowRotary(PositionEncoding):
+        def __init__(self, spec, prefix, tensors, runtime):
+            self.spec, self.rt, self.capacity = spec, runtime, 0
+            self.cos = self.sin = None
+
+        def prepare(self, capacity):
+            if capacity <= self.capacity:
+                return
+            rot = self.spec.rotary_dim
+            inv = 1.0 / np.power(float(self.spec.theta), 2.0 * np.arange(rot // 2, dtype=np.float64) / rot)
+            ang = (np.arange(capacity, dtype=np.float64) / self.spec.slowdown)[:, None] * inv[None, :]
+            self.cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(self.rt.device)
+            self.sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(self.rt.device)
+            self.capacity = capacity
+
+        def kernel_args(self):
+            return self.cos, self.sin, self.spec.rotary_dim
+    return SlowRotary
+
+
+@dataclass(frozen=True)
+class MixedConfig:
+    """Layer 0: built-in attention with the toy position encoding and the built-in SwiGLU.
+    Layer 1: built-in attention with the built-in rotary embedding and the toy routed feed-forward."""
+    hidden_size: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate_size: int
+    experts: int
+    inner: int
+    vocab_size: int
+    theta: float
+    slowdown: float
+    rms_norm_eps: float
+    max_position_embeddings: int = 2048
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(*[d[k] for k in ("hidden_size", "heads", "kv_heads", "head_dim", "intermediate_size", "experts", "inner",
+                                    "vocab_size", "theta", "slowdown", "rms_norm_eps")])
+
+    def to_dict(self):
+        d = {k: getattr(self, k) for k in ("hidden_size", "heads", "kv_heads", "head_dim", "intermediate_size", "experts", "inner",
+                                           "vocab_size", "theta", "slowdown", "rms_norm_eps")}
+        d.update(architectures=["ToyMixedForCausalLM"], model_type="toy_mixed")
+        return d
+
+    def model_spec(self):
+        from gophonic_b200.config import (AttentionSpec, EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, RMSNormSpec, RotarySpec,
+                                          SwiGLUSpec, default_schedule)
+        norm = RMSNormSpec(self.hidden_size, self.rms_norm_eps)
+        positions = [SlowRotarySpec(self.head_dim, self.head_dim, self.theta, self.slowdown), RotarySpec(self.head_dim, self.head_dim, self.theta)]
+        ffns = [SwiGLUSpec(self.hidden_size, self.intermediate_size), Top1Spec(self.hidden_size, self.experts, self.inner)]
+        layers = tuple(LayerSpec(prefix=f"m.layers.{i}.",
+                                 mixer=AttentionSpec(self.hidden_size, self.heads, self.kv_heads, self.head_dim, self.head_dim ** -0.5,
+                                                     positions[i], qk_norm=None),
+                                 feed_forward=ffns[i], mixer_norm=norm, feed_forward_norm=norm, mixer_prefix="attn.",
+                                 feed_forward_prefix="ffn.", mixer_norm_prefix="n1.", feed_forward_norm_prefix="n2.")
+                       for i in range(2))
+        return ModelSpec("ToyMixedForCausalLM", self.hidden_size, self.vocab_size, self.max_position_embeddings,
+                         EmbeddingSpec("m.embed.weight", self.vocab_size, self.hidden_size), layers, default_schedule(2), norm,
+                         "m.norm.weight", HeadSpec("m.head.weight", self.vocab_size, self.hidden_size, tied_to=None))
+
+
+def mixed_plain(toks, cfg: MixedConfig, w):
+    def attn(x, p, slowdown):
+        T = len(toks)
+        q = (x @ w[p + "q_proj.weight"].T).reshape(T, cfg.heads, cfg.head_dim)
+        k = (x @ w[p + "k_proj.weight"].T).reshape(T, cfg.kv_heads, cfg.head_dim)
+        v = (x @ w[p + "v_proj.weight"].T).reshape(T, cfg.kv_heads, cfg.head_dim)
+        half = cfg.head_dim // 2
+        inv = 1.0 / np.power(cfg.theta, 2.0 * np.arange(half) / cfg.head_dim)
+        ang = (np.arange(T) / slowdown)[:, None] * inv[None, :]
+        c, s = np.cos(ang).astype(np.float32).astype(np.float64)[:, None, :], np.sin(ang).astype(np.float32).astype(np.float64)[:, None, :]
+        rot = lambda y: np.concatenate([y[..., :half] * c - y[..., half:] * s, y[..., half:] * c + y[..., :half] * s], -1)
+        q, k = rot(q), rot(k)
+        out = np.zeros((T, cfg.heads, cfg.head_dim))
+        g = cfg.heads // cfg.kv_heads
+        for h in range(cfg.heads):
+            sc = (q[:, h] @ k[:, h // g].T) * cfg.head_dim ** -0.5
+            sc = np.where(np.tril(np.ones((T, T), bool)), sc, -np.inf)
+            pr = np.exp(sc - sc.max(-1, keepdims=True))
+            out[:, h] = (pr / pr.sum(-1, keepdims=True)) @ v[:, h // g]
+        return out.reshape(T, -1) @ w[p + "o_proj.weight"].T
+
+    h = P.embed(toks, w["m.embed.weight"])
+    for i in range(2):
+        p = f"m.layers.{i}."
+        h = h + attn(P.rms_norm(h, w[p + "n1.weight"], cfg.rms_norm_eps), p + "attn.", cfg.slowdown if i == 0 else 1.0)
+        x = P.rms_norm(h, w[p + "n2.weight"], cfg.rms_norm_eps)
+        if i == 0:
+            h = h + P.swiglu_ffn(x, w, p + "ffn.")
+        else:
+            logits = x @ w[p + "ffn.router.weight"].T
+            prob = np.exp(logits - logits.max(-1, keepdims=True))
+            prob /= prob.sum(-1, keepdims=True)
+            best = logits.argmax(-1)
+            y = np.zeros_like(x)
+            for t in range(len(toks)):
+                e = best[t]
+                y[t] = (np.maximum(x[t] @ w[p + f"ffn.experts.{e}.w1.weight"].T, 0) @ w[p + f"ffn.experts.{e}.w2.weight"].T) * prob[t, e]
+            h = h + y
+    return P.rms_norm(h, w["m.norm.weight"], cfg.rms_norm_eps) @ w["m.head.weight"].T
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_layer_by_layer(tmp_path):
+    """Two layers whose parts differ: the registry builds each from its spec's kind, the loader and
+    the random-weights writer work from the parts' declarations, the engine steps prompts and
+    single tokens, and the logits are those of a plain restatement.  In 32-bit, where the router's
+    choice cannot flip on rounding."""
+    from gophonic_b200 import registry
+    from gophonic_b200.engine import Engine, Model
+    from gophonic_b200.weights import InitScales, write_random_model
+    registry.register_feed_forward("toy-top1", _routed_ffn())
+    registry.register_position("toy-slow-rope", _slow_rope())
+    registry.register_architecture("ToyMixedForCausalLM", MixedConfig, model_type="toy_mixed")
+    cfg = MixedConfig(hidden_size=64, heads=4, kv_heads=2, head_dim=16, intermediate_size=96, experts=3, inner=40, vocab_size=211,
+                      theta=10000.0, slowdown=4.0, rms_norm_eps=1e-5)
+    d = str(tmp_path / "mixed")
+    write_random_model(cfg, 5, d, scales=InitScales(**TEST_SCALES))
+    assert registry.read_config(d) == cfg
+    model = Model.from_dir(d, dtype="float32")
+    assert not model.capturable  # the routed part reads device values on the host: steps run eagerly
+    eng = Engine(model, max_tokens=1024)
+    _, w = P.read_model(d)
+    rng = np.random.default_rng(2)
+    seqs = [rng.integers(0, 211, size=n).tolist() for n in (40, 9, 70)]
+    refs = [mixed_plain(s, cfg, w) for s in seqs]
+    slots = [eng.new_sequence() for _ in seqs]
+    cut = [30, 9, 5]
+    first = eng.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], [list(range(c)) for c in cut]).cpu().numpy()
+    got = [[first[sum(cut[:i]):sum(cut[:i + 1])]] for i in range(3)]
+    step = 0
+    while True:
+        live = [i for i in range(3) if cut[i] + step < len(seqs[i])]
+        if not live:
+            break
+        out = eng.step([(slots[i], [seqs[i][cut[i] + step]]) for i in live], [[0]] * len(live)).cpu().numpy()
+        for j, i in enumerate(live):
+            got[i].append(out[j:j + 1])
+        step += 1
+    for i in range(3):
+        assert rel(np.concatenate(got[i], 0), refs[i]) < TOL[torch.float32], i
+        eng.end_sequence(slots[i])
+    eng.cache.check()
