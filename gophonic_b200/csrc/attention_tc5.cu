@@ -6,9 +6,9 @@
 //     S_g = Q_g K^T   (M 128, N 64 keys, K 128)   -> two S buffers of 64 columns per group
 //     O_g += P_g V    (M 128, N 128, K 64 keys)    -> one O buffer of 128 columns per group
 // Roles by warp: warp 0 loads by TMA (the query tiles once; per page two boxes of keys and two of
-// values straight from the paged cache, three stages deep); one thread of warp 1 and one of warp 2
-// issue the products of group A and B; warps 3-6 and 7-10 are the softmax of group A and B: each
-// thread owns one query row, reads its row of S
+// values straight from the paged cache, three stages deep); one thread each of warps 1-2 issues the
+// scores products of group A and B and one each of warps 3-4 their values products; warps 5-8 and
+// 9-12 are the softmax of group A and B: each thread owns one query row, reads its row of S
 // from tensor memory, keeps the running maximum and sum, and writes the probabilities as bfloat16
 // into shared memory in the operand layout of the second product.  O stays in tensor memory and is
 // rescaled only when a row's maximum has grown by more than 2^8 since the scale in use was chosen
@@ -51,7 +51,8 @@ namespace {
 __device__ int g_status;
 
 typedef __nv_bfloat16 bf16;
-constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 3, THREADS = 352;
+constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 3, THREADS = 416;
+constexpr int FIRST_SOFTMAX_WARP = 1 + 2 * GROUPS;  // warp 0 loads, then a scores issuer and a values issuer per group
 constexpr int QPANEL = 128 * 128;               // 128 rows of 128 bytes (64 head elements)
 constexpr int KPANEL = 64 * 128;                // 64 keys of 128 bytes
 constexpr int Q_BYTES = 2 * QPANEL;             // one group's query tile
@@ -59,6 +60,7 @@ constexpr int P_BYTES = 128 * 128;              // one group's probabilities: 12
 constexpr int K_BYTES = 2 * KPANEL, V_BYTES = 2 * KPANEL, STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr int TMEM_COLS = 512;                  // S: 2 groups x 2 buffers x 64; O: 2 groups x 128
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int POLY_PAIRS = 2;                   // of every four pairs of scores, how many take the polynomial exponential
 constexpr float RESCALE_AT = 8.0f;              // rescale O when the row maximum outgrew the scale by 2^8
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -81,6 +83,56 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Packed pairs of fp32 (one instruction works on two values) and the three-input maximum: the
+// softmax warps set the pace of the kernel, so their instruction count matters.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t r, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(r)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2_down(uint64_t a, uint64_t b) {  // rounded towards minus infinity
+    uint64_t d;
+    asm("add.rm.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x of two values on the FMA pipe alone, for the share of the exponentials that the
+// special-function unit (16 a clock and SM) has no time for: x = n + f with n = floor(x) taken by
+// adding 1.5 * 2^23 rounded down, 2^f by a cubic (relative error 1.9e-4, a twentieth of the
+// bfloat16 step the probabilities are rounded to), and n added into the exponent field.
+__device__ __forceinline__ void exp2_poly_x2(float x0, float x1, float& y0, float& y1) {
+    x0 = fmaxf(x0, -126.f);
+    x1 = fmaxf(x1, -126.f);
+    const uint64_t x = pack2(x0, x1);
+    const uint64_t r = add2_down(x, pack2(12582912.f, 12582912.f));
+    const uint64_t n = add2(r, pack2(-12582912.f, -12582912.f));
+    const uint64_t f = fma2(n, pack2(-1.f, -1.f), x);
+    uint64_t q = fma2(f, pack2(0.0790199414f, 0.0790199414f), pack2(0.2241264433f, 0.2241264433f));
+    q = fma2(q, f, pack2(0.6968385577f, 0.6968385577f));
+    q = fma2(q, f, pack2(0.9998119473f, 0.9998119473f));
+    float q0, q1, r0, r1;
+    unpack2(q, q0, q1);
+    unpack2(r, r0, r1);
+    y0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    y1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
 }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -118,7 +170,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
     unsigned char* Ps = Qs + GROUPS * Q_BYTES;         // [GROUPS][2][P_BYTES]
     unsigned char* KVs = Ps + GROUPS * 2 * P_BYTES;    // [STAGES][K | V]
-    __shared__ uint64_t q_full, kv_full[STAGES], kv_empty[STAGES];
+    __shared__ uint64_t q_full, kv_full[STAGES], k_empty[STAGES], v_empty[STAGES];
     __shared__ uint64_t s_full[GROUPS][2], p_full[GROUPS][2], o_done[GROUPS][2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
@@ -162,7 +214,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         mbar_init(&q_full, 1);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], GROUPS);  // one arrival from each group's issuing thread
+            mbar_init(&k_empty[s], GROUPS);  // one arrival from each group's scores issuer
+            mbar_init(&v_empty[s], GROUPS);  // one arrival from each group's values issuer
         }
         for (int g = 0; g < GROUPS; g++) {
             for (int b = 0; b < 2; b++) {
@@ -197,7 +250,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             for (int j = 0; j < n; j++) {
                 const int s = j % STAGES;
                 const uint32_t phase = (uint32_t)(j / STAGES) & 1u;
-                if (!mbar_wait(&kv_empty[s], phase ^ 1u)) {
+                if (!mbar_wait(&k_empty[s], phase ^ 1u) || !mbar_wait(&v_empty[s], phase ^ 1u)) {
                     atomicCAS(&g_status, 0, 1);
                     abort_s = 1;
                 }
@@ -221,16 +274,17 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 mbar_wait(&q_full, 0);
             }
         }
-    } else if (warp <= GROUPS) {
-        // one issuing thread per group: waiting on a barrier and committing to one cost a few hundred
-        // cycles each on the issuing thread, so the groups do not share a thread
+    } else if (warp < FIRST_SOFTMAX_WARP) {
+        // Two issuing threads per group, in warps of their own: one issues the scores products, one
+        // the values products.  On an issuing thread a barrier wait that blocks and a commit cost a
+        // few hundred cycles each and a product about fifty, so a single thread doing both kinds
+        // (two or three waits, twelve products, three commits a page) set the pace of the kernel.
         if (lane == 0) {
-            const int g = warp - 1;
+            const int g = (warp - 1) % GROUPS;
+            const bool scores_role = warp - 1 < GROUPS;
             const int my_n = n_g[g];
-            const uint32_t idesc_qk = instr_desc(BQ, BKV);
-            const uint32_t idesc_pv = instr_desc(BQ, HD) | (1u << 16);  // values enter MN-major
-            bool ok = mbar_wait(&q_full, 0);
-            int kv_seen = -1;  // last page whose arrival has been waited for
+            bool ok = true;
+            int kv_seen = -1;  // last page whose arrival this thread has waited for
             auto need_page = [&](int j) -> bool {
                 while (kv_seen < j) {
                     kv_seen++;
@@ -238,53 +292,61 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 }
                 return true;
             };
-            // descriptors are built once and only advanced by constants in the loops
-            const uint64_t q_desc = smem_desc(s32(Qs + g * Q_BYTES));
-            uint64_t p_desc[2], k_desc[STAGES], v_desc[STAGES];
-            p_desc[0] = smem_desc(s32(Ps + (g * 2) * P_BYTES));
-            p_desc[1] = smem_desc(s32(Ps + (g * 2 + 1) * P_BYTES));
+            if (scores_role) {
+                // S_g[j & 1] = Q_g K_j^T, then the keys of page j are free
+                const uint32_t idesc_qk = instr_desc(BQ, BKV);
+                ok = mbar_wait(&q_full, 0);
+                const uint64_t q_desc = smem_desc(s32(Qs + g * Q_BYTES));
+                uint64_t k_desc[STAGES];
 #pragma unroll
-            for (int s = 0; s < STAGES; s++) {
-                k_desc[s] = smem_desc(s32(KVs + (size_t)s * STAGE_BYTES));
-                v_desc[s] = smem_desc_mn(s32(KVs + (size_t)s * STAGE_BYTES + K_BYTES));
-            }
-            // S_g[j & 1] = Q_g K_j^T.  The buffer is free: the softmax read S of page j - 2 before it
-            // announced the probabilities of that page, and this thread waited for those.
-            auto scores = [&](int j) -> bool {
-                const int b = j & 1;
-                if (!need_page(j)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint64_t kd = k_desc[j % STAGES];
-                const uint32_t d_tmem = tmem_base + (uint32_t)(g * 128 + b * 64);
+                for (int s = 0; s < STAGES; s++) k_desc[s] = smem_desc(s32(KVs + (size_t)s * STAGE_BYTES));
+                for (int j = 0; j < n && ok; j++) {
+                    // a group with fewer pages only keeps the count, but never ahead of the loads, or it
+                    // would arrive twice in one phase
+                    ok = need_page(j);
+                    if (ok && j < my_n) {
+                        const int b = j & 1;
+                        // the softmax has read S of page j - 2 out of this buffer once it has announced
+                        // the probabilities of that page
+                        if (j >= 2) ok = mbar_wait(&p_full[g][b], (uint32_t)((j - 2) >> 1) & 1u);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        const uint64_t kd = k_desc[j % STAGES];
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(g * 128 + b * 64);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {
-                    // 64 head elements to a panel; 16 elements = 32 bytes = 2 address units inside it
-                    umma(d_tmem, q_desc + (uint64_t)((ks >> 2) * (QPANEL >> 4) + (ks & 3) * 2),
-                         kd + (uint64_t)((ks >> 2) * (KPANEL >> 4) + (ks & 3) * 2), idesc_qk, ks > 0 ? 1u : 0u);
+                        for (int ks = 0; ks < HD / 16; ks++) {
+                            // 64 head elements to a panel; 16 elements = 32 bytes = 2 address units inside it
+                            umma(d_tmem, q_desc + (uint64_t)((ks >> 2) * (QPANEL >> 4) + (ks & 3) * 2),
+                                 kd + (uint64_t)((ks >> 2) * (KPANEL >> 4) + (ks & 3) * 2), idesc_qk, ks > 0 ? 1u : 0u);
+                        }
+                        umma_commit(&s_full[g][b]);
+                    }
+                    if (ok) umma_commit(&k_empty[j % STAGES]);
                 }
-                umma_commit(&s_full[g][b]);
-                return true;
-            };
-            auto values = [&](int j) -> bool {  // O_g (+)= P_g[j & 1] V_j
-                const int b = j & 1;
-                if (!mbar_wait(&p_full[g][b], (uint32_t)(j >> 1) & 1u)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint64_t pd = p_desc[b], vd = v_desc[j % STAGES];
-                const uint32_t d_tmem = tmem_base + (uint32_t)(256 + g * 128);
+            } else {
+                // O_g (+)= P_g[j & 1] V_j, then the values of page j are free
+                const uint32_t idesc_pv = instr_desc(BQ, HD) | (1u << 16);  // values enter MN-major
+                uint64_t p_desc[2], v_desc[STAGES];
+                p_desc[0] = smem_desc(s32(Ps + (g * 2) * P_BYTES));
+                p_desc[1] = smem_desc(s32(Ps + (g * 2 + 1) * P_BYTES));
 #pragma unroll
-                for (int kk = 0; kk < BKV / 16; kk++)  // 16 keys = 16 rows of 128 bytes further into the values
-                    umma(d_tmem, pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&o_done[g][b]);
-                return true;
-            };
-            if (ok && my_n > 0) ok = scores(0);
-            for (int j = 0; j < n && ok; j++) {
-                if (j + 1 < my_n) ok = scores(j + 1);
-                if (ok && j < my_n) ok = values(j);
-                // This group is done with page j.  A group with fewer pages only keeps the count, but
-                // it must not run ahead of the loads, or it would arrive twice in one phase.
-                if (ok && j >= my_n) ok = need_page(j);
-                if (ok) umma_commit(&kv_empty[j % STAGES]);
+                for (int s = 0; s < STAGES; s++) v_desc[s] = smem_desc_mn(s32(KVs + (size_t)s * STAGE_BYTES + K_BYTES));
+                for (int j = 0; j < n && ok; j++) {
+                    ok = need_page(j);
+                    if (ok && j < my_n) {
+                        const int b = j & 1;
+                        ok = mbar_wait(&p_full[g][b], (uint32_t)(j >> 1) & 1u);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        const uint64_t pd = p_desc[b], vd = v_desc[j % STAGES];
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(256 + g * 128);
+#pragma unroll
+                        for (int kk = 0; kk < BKV / 16; kk++)  // 16 keys = 16 rows of 128 bytes further into the values
+                            umma(d_tmem, pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(&o_done[g][b]);
+                    }
+                    if (ok) umma_commit(&v_empty[j % STAGES]);
+                }
             }
             if (!ok) {
                 atomicCAS(&g_status, 0, 3);
@@ -293,7 +355,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         }
     } else {
         // softmax: group g, thread = query row
-        const int g = (warp - 1 - GROUPS) >> 2;
+        const int g = (warp - FIRST_SOFTMAX_WARP) >> 2;
         const int quad = warp & 3;
         const int r = quad * 32 + lane;               // row within the group
         const int qrow = q0 + g * BQ + r;             // row within the sequence's new rows
@@ -333,7 +395,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) mx[e] = fmaxf(mx[e], fmaxf(__uint_as_float(v0[i + e]), __uint_as_float(v1[i + e])));
+                for (int e = 0; e < 4; e++) mx[e] = max3(mx[e], __uint_as_float(v0[i + e]), __uint_as_float(v1[i + e]));
             }
             const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;  // sc > 0
             m_run = fmaxf(m_run, tile_max);
@@ -344,6 +406,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 ok = false;
                 break;
             }
+
             unsigned char* Pg = Ps + (g * 2 + b) * P_BYTES;
             if (__any_sync(0xffffffffu, grow && j > 0)) {
                 // O_g may only be touched between products: wait for the previous page's
@@ -366,7 +429,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             }
             if (grow) m_used = m_run;
             const float mbase = m_used == -INFINITY ? 0.f : m_used;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint64_t sc2 = pack2(sc, sc), nmb2 = pack2(-mbase, -mbase);
+            uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
             for (int c = 0; c < 8; c++) {  // eight 16-byte chunks of eight keys
                 uint32_t pk[4];
@@ -374,8 +438,15 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 for (int e = 0; e < 4; e++) {
                     const int i = (c & 3) * 8 + e * 2;
                     const uint32_t a = c < 4 ? v0[i] : v1[i], bb = c < 4 ? v0[i + 1] : v1[i + 1];
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(a), sc, -mbase)), p1 = fast_exp2(fmaf(__uint_as_float(bb), sc, -mbase));
-                    sum[e] += p0 + p1;
+                    float t0, t1, p0, p1;
+                    unpack2(fma2(pack2(__uint_as_float(a), __uint_as_float(bb)), sc2, nmb2), t0, t1);
+                    if (e < POLY_PAIRS) {
+                        exp2_poly_x2(t0, t1, p0, p1);
+                    } else {
+                        p0 = fast_exp2(t0);
+                        p1 = fast_exp2(t1);
+                    }
+                    sum2[e & 1] = add2(sum2[e & 1], pack2(p0, p1));
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                     pk[e] = *reinterpret_cast<uint32_t*>(&h2);
                 }
@@ -383,6 +454,9 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 unsigned char* dst = Pg + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
                 *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
+            float sum[4];
+            unpack2(sum2[0], sum[0], sum[1]);
+            unpack2(sum2[1], sum[2], sum[3]);
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
