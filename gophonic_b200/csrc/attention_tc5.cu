@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             for (int j = 0; j < n; j++) {
                 const int s = j % STAGES;
                 const uint32_t phase = (uint32_t)(j / STAGES) & 1u;
-                if (!mbar_wait(&k_empty[s], phase ^ 1u) || !mbar_wait(&v_empty[s], phase ^ 1u)) {
+                if (!mbar_wait_relaxed(&k_empty[s], phase ^ 1u) || !mbar_wait_relaxed(&v_empty[s], phase ^ 1u)) {
                     atomicCAS(&g_status, 0, 1);
                     abort_s = 1;
                 }
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             auto need_page = [&](int j) -> bool {
                 while (kv_seen < j) {
                     kv_seen++;
-                    if (!mbar_wait(&kv_full[kv_seen % STAGES], (uint32_t)(kv_seen / STAGES) & 1u)) return false;
+                    if (!mbar_wait_relaxed(&kv_full[kv_seen % STAGES], (uint32_t)(kv_seen / STAGES) & 1u)) return false;
                 }
                 return true;
             };
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                         const int b = j & 1;
                         // the softmax has read S of page j - 2 out of this buffer once it has announced
                         // the probabilities of that page
-                        if (j >= 2) ok = mbar_wait(&p_full[g][b], (uint32_t)((j - 2) >> 1) & 1u);
+                        if (j >= 2) ok = mbar_wait_relaxed(&p_full[g][b], (uint32_t)((j - 2) >> 1) & 1u);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                         const uint64_t kd = k_desc[j % STAGES];

@@ -35,6 +35,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+// The same wait for a thread that is not on the critical path (a loader that runs ahead): it sleeps
+// between polls, so that its polling does not take issue slots from the warps that compute.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+    uint32_t done = 0;
+    for (unsigned i = 0; i < TC5_SPIN_LIMIT; i++) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(s32(bar)), "r"(parity)
+            : "memory");
+        if (done) return true;
+        __nanosleep(64);
+    }
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(s32(smem_dst)),
