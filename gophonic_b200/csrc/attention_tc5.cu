@@ -5,8 +5,8 @@
 // with the accumulators in tensor memory:
 //     S_g = Q_g K^T   (M 128, N 64 keys, K 128)   -> two S buffers of 64 columns per group
 //     O_g += P_g V    (M 128, N 128, K 64 keys)    -> one O buffer of 128 columns per group
-// Roles by warp: warp 0 loads by TMA (the query tiles once; per page two boxes of keys and two of
-// values straight from the paged cache, three stages deep); one thread each of warps 1-2 issues the
+// Roles by warp: warp 0 loads the query tiles once and per page two boxes of keys, the last warp per
+// page two boxes of values, by TMA straight from the paged cache, three pages deep each; one thread each of warps 1-2 issues the
 // scores products of group A and B and one each of warps 3-4 their values products; warps 5-8 and
 // 9-12 are the softmax of group A and B: each thread owns one query row, reads its row of S
 // from tensor memory, keeps the running maximum and sum, and writes the probabilities as bfloat16
@@ -51,8 +51,9 @@ namespace {
 __device__ int g_status;
 
 typedef __nv_bfloat16 bf16;
-constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 3, THREADS = 416;
-constexpr int FIRST_SOFTMAX_WARP = 1 + 2 * GROUPS;  // warp 0 loads, then a scores issuer and a values issuer per group
+constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 3, THREADS = 448;
+constexpr int FIRST_SOFTMAX_WARP = 1 + 2 * GROUPS;  // warp 0 loads queries and keys, then a scores issuer and a values issuer per group
+constexpr int VALUE_LOADER_WARP = FIRST_SOFTMAX_WARP + 4 * GROUPS;  // the last warp loads the values
 constexpr int QPANEL = 128 * 128;               // 128 rows of 128 bytes (64 head elements)
 constexpr int KPANEL = 64 * 128;                // 64 keys of 128 bytes
 constexpr int Q_BYTES = 2 * QPANEL;             // one group's query tile
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
     unsigned char* Ps = Qs + GROUPS * Q_BYTES;         // [GROUPS][2][P_BYTES]
     unsigned char* KVs = Ps + GROUPS * 2 * P_BYTES;    // [STAGES][K | V]
-    __shared__ uint64_t q_full, kv_full[STAGES], k_empty[STAGES], v_empty[STAGES];
+    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES];
     __shared__ uint64_t s_full[GROUPS][2], p_full[GROUPS][2], o_done[GROUPS][2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
@@ -213,7 +214,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&kv_full[s], 1);
+            mbar_init(&k_full[s], 1);
+            mbar_init(&v_full[s], 1);
             mbar_init(&k_empty[s], GROUPS);  // one arrival from each group's scores issuer
             mbar_init(&v_empty[s], GROUPS);  // one arrival from each group's values issuer
         }
@@ -246,32 +248,56 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 tma_load_2d(Qs + g * Q_BYTES, &map_q, head * HD, q_start + q0 + g * BQ, &q_full);
                 tma_load_2d(Qs + g * Q_BYTES + QPANEL, &map_q, head * HD + 64, q_start + q0 + g * BQ, &q_full);
             }
+            // Keys and values travel separately: the keys of a page are free as soon as its scores are
+            // done, long before its values are, so the key loads run further ahead than a shared
+            // ring would let them, and the scores issuer never waits for them.
             int issued = 0;
             for (int j = 0; j < n; j++) {
                 const int s = j % STAGES;
                 const uint32_t phase = (uint32_t)(j / STAGES) & 1u;
-                if (!mbar_wait_relaxed(&k_empty[s], phase ^ 1u) || !mbar_wait_relaxed(&v_empty[s], phase ^ 1u)) {
+                if (!mbar_wait_relaxed(&k_empty[s], phase ^ 1u)) {
                     atomicCAS(&g_status, 0, 1);
                     abort_s = 1;
                 }
                 if (*(volatile int*)&abort_s) break;
-                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+                mbar_expect_tx(&k_full[s], K_BYTES);
                 unsigned char* ks = KVs + (size_t)s * STAGE_BYTES;
-                unsigned char* vs = ks + K_BYTES;
                 int lp = t_lo + j;
                 if (lp >= p.bt_stride) lp = p.bt_stride - 1;
                 const int row = (bt[lp] * p.kv_heads + kvh) * 64;
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    tma_load_2d(ks + h * KPANEL, &map_k, h * 64, row, &kv_full[s]);
-                    tma_load_2d(vs + h * KPANEL, &map_v, h * 64, row, &kv_full[s]);
-                }
+                for (int h = 0; h < 2; h++) tma_load_2d(ks + h * KPANEL, &map_k, h * 64, row, &k_full[s]);
                 issued = j + 1;
             }
             if (*(volatile int*)&abort_s) {
                 for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++)
-                    mbar_wait(&kv_full[j % STAGES], (uint32_t)(j / STAGES) & 1u);
+                    mbar_wait(&k_full[j % STAGES], (uint32_t)(j / STAGES) & 1u);
                 mbar_wait(&q_full, 0);
+            }
+        }
+    } else if (warp == VALUE_LOADER_WARP) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int j = 0; j < n; j++) {
+                const int s = j % STAGES;
+                const uint32_t phase = (uint32_t)(j / STAGES) & 1u;
+                if (!mbar_wait_relaxed(&v_empty[s], phase ^ 1u)) {
+                    atomicCAS(&g_status, 0, 1);
+                    abort_s = 1;
+                }
+                if (*(volatile int*)&abort_s) break;
+                mbar_expect_tx(&v_full[s], V_BYTES);
+                unsigned char* vs = KVs + (size_t)s * STAGE_BYTES + K_BYTES;
+                int lp = t_lo + j;
+                if (lp >= p.bt_stride) lp = p.bt_stride - 1;
+                const int row = (bt[lp] * p.kv_heads + kvh) * 64;
+#pragma unroll
+                for (int h = 0; h < 2; h++) tma_load_2d(vs + h * KPANEL, &map_v, h * 64, row, &v_full[s]);
+                issued = j + 1;
+            }
+            if (*(volatile int*)&abort_s) {
+                for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; j++)
+                    mbar_wait(&v_full[j % STAGES], (uint32_t)(j / STAGES) & 1u);
             }
         }
     } else if (warp < FIRST_SOFTMAX_WARP) {
@@ -288,7 +314,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             auto need_page = [&](int j) -> bool {
                 while (kv_seen < j) {
                     kv_seen++;
-                    if (!mbar_wait_relaxed(&kv_full[kv_seen % STAGES], (uint32_t)(kv_seen / STAGES) & 1u)) return false;
+                    uint64_t* full = scores_role ? &k_full[kv_seen % STAGES] : &v_full[kv_seen % STAGES];
+                    if (!mbar_wait_relaxed(full, (uint32_t)(kv_seen / STAGES) & 1u)) return false;
                 }
                 return true;
             };
