@@ -130,7 +130,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) 
 def gemm_add_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     """Whether ``gemm_add`` takes this product: a prompt-sized bfloat16 product into a float32 ``out``."""
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.float32 and a.dim() == 2
-            and a.shape[0] >= TC5_PAIR_MIN_ROWS and _has("gb_gemm_tc5_pair_add") and w.is_contiguous() and tc5_accepts(a, w, out))
+            and a.shape[0] >= TC5_PAIR_MIN_ROWS and w.is_contiguous() and tc5_accepts(a, w, out))
 
 
 def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -150,7 +150,7 @@ def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gemm_swiglu_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether ``gemm_swiglu`` takes this product: bfloat16, interleaved gate/up rows, and a row
     count one of the kernels with the fused epilogue handles (up to 64, or at least 128)."""
-    return (_has("gb_gemm_skinny_swiglu") and (a.shape[0] <= 64 or (a.shape[0] >= 128 and _has("gb_gemm_tc5_swiglu")))
+    return ((a.shape[0] <= 64 or a.shape[0] >= 128)
             and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and w.shape[0] % 16 == 0 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
@@ -166,7 +166,7 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2) or out.stride(1) != 1 or not gemm_swiglu_accepts(a, w):
         raise KernelError(f"gemm_swiglu: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    if M >= TC5_PAIR_MIN_ROWS and algo != "tc5" and _has("gb_gemm_tc5_pair_swiglu") or algo == "tc5_pair":
+    if M >= TC5_PAIR_MIN_ROWS and algo != "tc5" or algo == "tc5_pair":
         _check(_lib.gb_gemm_tc5_pair_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                             c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
         return
@@ -174,7 +174,7 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
         _check(_lib.gb_gemm_tc5_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                        c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
         return
-    if M > SKINNY_MAX_ROWS and algo != "skinny" and _has("gb_gemm_tc5_decode") or algo == "tc5_decode":
+    if M > SKINNY_MAX_ROWS and algo != "skinny" or algo == "tc5_decode":
         _tc5_decode(a, w, out, 1)
         return
     _check(_lib.gb_gemm_skinny_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
@@ -196,17 +196,14 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                              c_int64(out.stride(0)), _stream()))
 
 
-def _has(name: str) -> bool:
-    return hasattr(_lib, name)
-
-
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto") -> str:
     """out = a @ w^T, choosing the kernel by operand types and sizes.  Returns the kernel's name.
 
-    bfloat16 activations with bfloat16 weights go to the tensor-core kernels (a weight-streaming
-    kernel for up to 64 rows, tiled kernels above); everything else, and every shape those
-    kernels refuse, goes to the fp32 CUDA-core kernel.  float32 operands never touch a tensor
-    core.
+    bfloat16 activations with bfloat16 weights go to the tensor-core kernels: up to 8 rows the
+    fragment-streaming kernel, up to 64 the tcgen05 decode kernel, 65 to 127 mma.sync tiles, from 128
+    the tiled tcgen05 kernel and from 192 the one that pairs two SMs on a tile.  Everything else,
+    and operands whose rows are not 16-byte aligned, goes to the fp32 CUDA-core kernel.  float32
+    operands never touch a tensor core.
     """
     _need(a, "gemm a", dim=2, contiguous=False)
     _need(w, "gemm w", dim=2)
@@ -226,20 +223,16 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
         gemm_simt(a, w, out)
         return "simt"
     if algo == "auto":
-        if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT and _has("gb_gemm_skinny"):
-            algo = "skinny"
-        elif M <= 64 and _has("gb_gemm_tc5_decode"):
-            algo = "tc5_decode"
-        elif M <= 64 and _has("gb_gemm_skinny"):
-            algo = "skinny"
-        elif _has("gb_gemm_tc5_pair") and M >= TC5_PAIR_MIN_ROWS and tc5_accepts(a, w, out):
-            algo = "tc5_pair"
-        elif _has("gb_gemm_tc5") and M >= 128 and tc5_accepts(a, w, out):
-            algo = "tc5"
-        elif _has("gb_gemm_mma"):
-            algo = "mma"
+        if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT:
+            algo = "skinny"        # weights streamed straight into mma.sync fragments
+        elif M <= 64:
+            algo = "tc5_decode"    # tcgen05, weights on the M side, K slices across a cluster
+        elif M >= TC5_PAIR_MIN_ROWS:
+            algo = "tc5_pair"      # tcgen05 on pairs of SMs, 256 x 256 tiles
+        elif M >= 128:
+            algo = "tc5"           # tcgen05, 128 x 256 tiles
         else:
-            algo = "simt"
+            algo = "mma"           # mma.sync tiles
     if algo == "skinny":
         _check(_lib.gb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                    c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
@@ -294,8 +287,7 @@ def tc5_status() -> int:
     """0, or which role of a tcgen05 kernel gave up waiting on a barrier since the last call."""
     code = 0
     for name in ("gb_gemm_tc5_status", "gb_gemm_tc5_decode_status", "gb_attention_tc5_status"):
-        if _has(name):
-            code = code or int(getattr(_lib, name)())
+        code = code or int(getattr(_lib, name)())
     return code
 
 
@@ -404,12 +396,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
     if algo == "auto":
         algo = "simt"
         if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and (head_dim <= 128 or head_dim == 256) and ring_pages == 0:
-            if max_q_len == 1 and _has("gb_attention_decode_mma"):
+            if max_q_len == 1:
                 algo = "decode_mma"
-            elif (max_q_len >= TC5_ATTENTION_MIN_ROWS and head_dim == 128 and _has("gb_attention_prefill_tc5")
+            elif (max_q_len >= TC5_ATTENTION_MIN_ROWS and head_dim == 128
                   and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0):
                 algo = "prefill_tc5"
-            elif max_q_len > 1 and _has("gb_attention_prefill_mma"):
+            else:
                 algo = "prefill_mma"
     nk = 2 if num_splits > 1 else 1
     if algo == "simt":

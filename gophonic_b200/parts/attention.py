@@ -71,7 +71,7 @@ class Attention(Mixer):
     def adds_in_place(self, rows: int) -> bool:
         ops = self.rt.ops
         return (self.o.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.q_dim % 8 == 0
-                and hasattr(ops, "gemm_add") and rows >= ops.TC5_PAIR_MIN_ROWS)
+                and rows >= ops.TC5_PAIR_MIN_ROWS)
 
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
         self.rt.ops.gemm_add(self._context(batch, x, cache), self.o, h)
