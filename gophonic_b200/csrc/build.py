@@ -171,11 +171,13 @@ def ensure_built(verbose: bool = True, extra_flags: Optional[List[str]] = None) 
             json.dump({"digest": digest, "flags": flags, "sources": sources}, f)
     finally:
         done.set()
-        for o in objs:
-            try:
-                os.remove(o)
-            except OSError:
-                pass
+        # this build's objects, also those of sources that compiled before another one failed
+        for name in os.listdir(bdir):
+            if name.endswith(f".{tag}.o") or name.endswith(f".{tag}.tmp"):
+                try:
+                    os.remove(os.path.join(bdir, name))
+                except OSError:
+                    pass
     _say(f"kernel library ready after {time.time() - t0:.0f} s", verbose)
     return os.path.join(bdir, LIB_NAME)
 
