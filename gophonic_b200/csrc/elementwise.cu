@@ -48,6 +48,23 @@ GB_API int gb_embed_gather(const void* table, int table_dtype, const int* ids, i
     return 0;
 }
 
+// ids[i] = source[ids[i]]: a step whose tokens are the ones the sampler just left on the device takes
+// them by position, so the host need not have read them.  A position outside the source gives 0.
+__global__ void gather_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, int n, int source_n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int p = ids[i];
+    ids[i] = (p >= 0 && p < source_n) ? source[p] : 0;
+}
+
+GB_API int gb_gather_tokens(int* ids, const int* source, int n, int source_n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (source_n <= 0) GB_REFUSE("gather_tokens: empty source");
+    gather_tokens_kernel<<<ceil_div(n, 128), 128, 0, stream>>>(ids, source, n, source_n);
+    GB_CHECK_LAUNCH("gather_tokens");
+    return 0;
+}
+
 // ------------------------------------------------------------------------------------------
 // residual add + RMSNorm                     (internal/qwen3lm/ops.go:94-108, 251-254)
 //   v = h[row] (+ delta[row]);  if the rows are not gathered, h[row] = v

@@ -11,6 +11,13 @@ empty the next one starts, reusing the slots, until no request is left.
 The loop decides; it computes nothing.  It talks to an *engine* (``new_sequence``, ``step``,
 ``end_sequence``, ``room``) and a *sampler* (``start``, ``select``), so its decisions are tested
 without a GPU.
+
+If the engine can take a step's tokens from where the sampler left them (``step_from``,
+``fetch_tokens``) and the sampler can leave them there (``select_device``), the loop runs one step
+ahead of what it has read: step k + 1 is enqueued for every sequence that step k cannot end by
+length, then the tokens of step k are read and handled while step k + 1 runs.  A sequence that
+drew a stop token in step k has then run one step for nothing; its result is dropped.  Replies,
+callbacks and their order are the same as without the overlap.
 """
 from __future__ import annotations
 
@@ -118,6 +125,8 @@ class Generator:
         return results
 
     def _run_batch(self, batch: List[Request], on_token) -> None:
+        if all(hasattr(self.engine, a) for a in ("step_from", "fetch_tokens")) and hasattr(self.sampler, "select_device"):
+            return self._run_batch_ahead(batch, on_token)
         self.stats.batches += 1
         live: List[Request] = []
         try:
@@ -146,6 +155,55 @@ class Generator:
                 logits = self.engine.step([(r.slot, [r.reply[-1]]) for r in live])
                 self.stats.decode_steps += 1
                 self.stats.decoded_tokens += len(live)
+        finally:
+            for r in batch:
+                if r.slot is not None:
+                    self.engine.end_sequence(r.slot)
+                    r.slot = None
+
+    def _run_batch_ahead(self, batch: List[Request], on_token) -> None:
+        """The same batch with the next step enqueued before the last one's tokens are read."""
+        self.stats.batches += 1
+        try:
+            live: List[Request] = []
+            for row, r in enumerate(batch):
+                r.slot = self.engine.new_sequence()
+                r.row = row
+                self.sampler.start(row, r.options, r.seed)
+                live.append(r)
+            logits = self.engine.step([(r.slot, r.prompt) for r in live])
+            self.stats.prefill_tokens += sum(len(r.prompt) for r in live)
+            drawn = self.sampler.select_device(logits, [r.row for r in live])   # tokens of `live`, on the device
+            fetch = self.engine.fetch_tokens(drawn)
+            while True:
+                # `drawn` holds the unread tokens of `live`, in order (entries of sequences that ended a
+                # step ago are there too and are skipped).  Who goes on if nobody draws a stop token:
+                # everyone whose reply the unread token does not fill.
+                ahead = [(i, r) for i, r in enumerate(live) if r.finished is None and len(r.reply) + 1 < r.budget]
+                nxt = None
+                if ahead:
+                    logits = self.engine.step_from([r.slot for _, r in ahead], drawn, [i for i, _ in ahead])
+                    nxt_drawn = self.sampler.select_device(logits, [r.row for _, r in ahead])
+                    nxt = ([r for _, r in ahead], nxt_drawn, self.engine.fetch_tokens(nxt_drawn))
+                # read and handle the tokens of the step before while the one just enqueued runs
+                going = 0
+                for r, t in zip(live, fetch.wait()):
+                    if r.finished is not None:
+                        continue  # it drew a stop token a step ago: this entry ran for nothing
+                    self._take(r, int(t), on_token)
+                    if r.finished is None:
+                        going += 1
+                    else:
+                        self.engine.end_sequence(r.slot)
+                        r.slot = None
+                if nxt is None:
+                    break
+                live, drawn, fetch = nxt
+                if going == 0:
+                    fetch.wait()  # every sequence of the enqueued step has ended: its tokens are dropped
+                    break
+                self.stats.decode_steps += 1
+                self.stats.decoded_tokens += going
         finally:
             for r in batch:
                 if r.slot is not None:

@@ -108,6 +108,18 @@ class HostStager:
         self.bytes_uploaded += 4 * n
 
 
+class TokenFetch:
+    """Tokens on their way from the device to the host: a pinned buffer and the event of its copy."""
+
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event):
+        self.host = host
+        self.event = event
+
+    def wait(self) -> List[int]:
+        self.event.synchronize()
+        return self.host.tolist()
+
+
 def build_batch(pieces: Sequence[Tuple[int, Sequence[int], int]], device, sm_count: int = 148,
                 want_rows: Optional[Sequence[int]] = None,
                 stager: Optional[HostStager] = None) -> Tuple[StepBatch, Optional[torch.Tensor]]:
@@ -170,6 +182,8 @@ class Engine:
         self.vocab = model.spec.vocab
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.stager = HostStager(self.device)
+        self._fetch_bufs: List[Optional[torch.Tensor]] = [None] * 4
+        self._fetch_at = 0
         self.passes = 0
         self.graphs = None
         if use_graphs and model.capturable:
@@ -257,13 +271,58 @@ class Engine:
         self.cache.commit(grow)
         return logits
 
-    def _pass(self, pieces, want_rows: Sequence[int]) -> Optional[torch.Tensor]:
+    def step_from(self, slots: Sequence[int], source: torch.Tensor, positions: Sequence[int]) -> torch.Tensor:
+        """One token each: sequence ``slots[i]`` goes on by ``source[positions[i]]``, where ``source``
+        is a device int32 tensor (what the sampler left for the step before).  The host need not
+        have read the tokens, so this step can be enqueued while the last one still runs.  Returns
+        fp32 logits [len(slots), vocab]."""
+        if source.dtype != torch.int32 or source.dim() != 1 or source.device != self.device:
+            raise StepError("step_from: the token source must be a 1-d int32 tensor on the engine's device")
+        if len(slots) != len(positions) or not slots:
+            raise StepError(f"step_from: {len(slots)} slots, {len(positions)} positions")
+        for p in positions:
+            if not 0 <= int(p) < source.numel():
+                raise StepError(f"step_from: position {p} is outside the source of {source.numel()} tokens")
+        # the positions stand where token ids would; validation of ids is the sampler's guarantee
+        entries = [(slot, [0]) for slot in slots]
+        self.validate(entries, None)
+        entries = [(slot, [int(p)]) for slot, p in zip(slots, positions)]
+        grow = [(slot, self.cache.length(slot) + 1) for slot in slots]
+        self.cache.reserve(grow)
+        n = len(entries)
+        if self.graphs is not None and n <= self.graphs.max_batch:
+            logits = self._graph_pass(entries, source)
+        elif n <= self.max_rows_per_pass:
+            pieces = [(slot, toks, self.cache.length(slot)) for slot, toks in entries]
+            logits = self._pass(pieces, list(range(n)), source)
+        else:
+            raise StepError(f"step_from: {n} sequences exceed one pass of {self.max_rows_per_pass} rows")
+        self.cache.commit(grow)
+        return logits
+
+    def fetch_tokens(self, tokens: torch.Tensor) -> TokenFetch:
+        """Start copying a device int32 tensor of tokens to pinned host memory; ``wait()`` on the
+        result gives them as a list once the copy has happened."""
+        n = tokens.numel()
+        i = self._fetch_at
+        self._fetch_at = (i + 1) % len(self._fetch_bufs)
+        if self._fetch_bufs[i] is None or self._fetch_bufs[i].numel() < n:
+            self._fetch_bufs[i] = torch.empty(max(256, 2 * n), dtype=torch.int32).pin_memory()
+        host = self._fetch_bufs[i][:n]
+        host.copy_(tokens, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return TokenFetch(host, ev)
+
+    def _pass(self, pieces, want_rows: Sequence[int], source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         batch, want_dev = build_batch(pieces, self.device, self.sm_count, want_rows if want_rows else None,
                                       self.stager)
+        if source is not None:
+            self.model.rt.ops.gather_tokens(batch.ids, source)
         self.passes += 1
         return self.model.forward(batch, self.cache, want_dev)
 
-    def _graph_pass(self, entries) -> torch.Tensor:
+    def _graph_pass(self, entries, source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One token each, every row wanted: replay the captured step."""
         n = len(entries)
         firsts = [self.cache.length(slot) for slot, _ in entries]
@@ -271,9 +330,13 @@ class Engine:
         if g.logits is None:
             # the capture runs the step's kernels on the graph's own input buffer: fill it first
             self._fill_graph_meta(g, entries, firsts)
+            if source is not None:
+                self.model.rt.ops.gather_tokens(g.meta[:n], source)
             torch.cuda.synchronize()
             g.capture()
         self._fill_graph_meta(g, entries, firsts)
+        if source is not None:
+            self.model.rt.ops.gather_tokens(g.meta[:n], source)  # the ids section held positions
         self.passes += 1
         return g.replay()
 

@@ -82,6 +82,13 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> N
 
 
 # ---- norm --------------------------------------------------------------------------------
+def gather_tokens(ids: torch.Tensor, source: torch.Tensor) -> None:
+    """ids[i] = source[ids[i]] in place (both int32 on the device)."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(source, "token source", torch.int32, 1)
+    _check(_lib.gb_gather_tokens(_ptr(ids), _ptr(source), c_int(ids.numel()), c_int(source.numel()), _stream()))
+
+
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
     """h += delta (if given, in place, unless ``rows`` selects); out = rmsnorm(h) * weight."""

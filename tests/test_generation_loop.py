@@ -157,3 +157,77 @@ def test_on_token_streams_in_order():
     g = Generator(eng, ScriptSampler({0: [5, 6], 1: [7]}), 4, 100, (99,))
     g.generate([[1], [2]], on_token=lambda i, t: got.append((i, t)))
     assert got == [(0, 5), (1, 7), (0, 6)]
+
+
+# ---- the loop that runs one step ahead of what it has read --------------------------------------
+class AheadEngine(ScriptEngine):
+    """The scripted engine with the two calls that let the loop enqueue a step before it has read
+    the last one's tokens.  ``wasted`` counts entries stepped for a sequence that had already
+    drawn its stop token."""
+
+    def __init__(self, pages=100):
+        super().__init__(pages)
+        self.unread = 0      # fetches started and not yet waited for
+        self.max_unread = 0
+
+    def step_from(self, slots, source, positions):
+        assert len(slots) == len(positions) and len(set(slots)) == len(slots)
+        return self.step([(s, [source[p]]) for s, p in zip(slots, positions)])
+
+    def fetch_tokens(self, tokens):
+        eng = self
+        eng.unread += 1
+        eng.max_unread = max(eng.max_unread, eng.unread)
+
+        class Fetch:
+            def wait(self_inner):
+                eng.unread -= 1
+                return list(tokens)
+        return Fetch()
+
+
+class AheadSampler(ScriptSampler):
+    def select_device(self, logits, rows):
+        return self.select(logits, rows)
+
+
+def run_ahead(prompts, scripts, max_batch=4, context=1000, options=None, pages=100, stop=(99,), on_token=None):
+    eng = AheadEngine(pages)
+    g = Generator(eng, AheadSampler(scripts), max_batch, context, stop)
+    return g.generate(prompts, options, on_token), eng, g
+
+
+CASES = [
+    ([[1, 2, 3]], {0: [5, 6, 7]}, {}),
+    ([[1], [2, 2], [3, 3, 3]], {0: [10], 1: [20, 21, 22], 2: []}, {}),
+    ([[1, 1]], {0: [5, 6, 7, 8]}, dict(options=Options(MaxTokens=2))),
+    ([[1] * 8], {0: list(range(10, 30))}, dict(context=11)),
+    ([[i + 1] for i in range(5)], {i: [100 + i] * (i + 1) for i in range(5)}, dict(max_batch=2)),
+    ([[1] * 64, [2] * 64, [3] * 64], {0: [7], 1: [8], 2: [9]}, dict(max_batch=4, pages=5, options=Options(MaxTokens=64))),
+    ([[4], [5]], {0: [1] * 30, 1: [2] * 3}, dict(options=[Options(MaxTokens=7), Options(MaxTokens=50)])),
+]
+
+
+@pytest.mark.parametrize("prompts,scripts,kw", CASES)
+def test_running_ahead_gives_the_same_replies_callbacks_and_counts(prompts, scripts, kw):
+    plain_calls, ahead_calls = [], []
+    g0 = Generator(ScriptEngine(kw.get("pages", 100)), ScriptSampler(scripts), kw.get("max_batch", 4), kw.get("context", 1000), (99,))
+    want = g0.generate(prompts, kw.get("options"), lambda i, t: plain_calls.append((i, t)))
+    got, eng, g = run_ahead(prompts, scripts, on_token=lambda i, t: ahead_calls.append((i, t)), **kw)
+    assert got == want
+    assert ahead_calls == plain_calls                       # every token, in the same order
+    assert not eng.held and eng.unread == 0                 # every slot given back, every fetch read
+    assert eng.max_unread <= 2                              # one step ahead, never more
+    s0, s1 = g0.stats, g.stats
+    assert (s1.batches, s1.prefill_tokens, s1.decode_steps, s1.decoded_tokens) == (s0.batches, s0.prefill_tokens, s0.decode_steps, s0.decoded_tokens)
+
+
+def test_running_ahead_wastes_one_entry_per_stop_token_and_none_per_length_end():
+    # request 0 stops by its stop token after 3 tokens: the step enqueued before that was read fed it
+    # once for nothing; request 1 ends by MaxTokens, which the loop knows beforehand
+    got, eng, _ = run_ahead([[1], [2]], {0: [10, 11, 12], 1: [20] * 40}, options=[Options(), Options(MaxTokens=5)])
+    assert got == [[10, 11, 12], [20] * 5]
+    fed0 = [t for st in eng.steps[1:] for s, t in st if s == eng.steps[0][0][0]]
+    fed1 = [t for st in eng.steps[1:] for s, t in st if s == eng.steps[0][1][0]]
+    assert fed0 == [[10], [11], [12], [99]]   # the stop token itself went through one step, its result dropped
+    assert fed1 == [[20]] * 4                 # the fifth token is drawn and never fed
