@@ -39,7 +39,14 @@ def _code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """torch's current CUDA stream of the current device, as a raw handle (asked anew at every call:
+    a graph capture runs on a stream of its own)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
