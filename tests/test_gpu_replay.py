@@ -298,6 +298,40 @@ def test_where_a_sequence_lies_in_the_cache_changes_nothing(engines, plain_model
     assert np.max(np.abs(a - b)) <= 1e-5 * np.max(np.abs(a))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_that_takes_its_tokens_from_the_device_equals_one_given_them(engines, plain_models, dtype):
+    """``step_from``: the tokens a sampler left on the device, picked by position (some skipped, as
+    when a sequence has ended), give the same bits as the same tokens handed over from the host,
+    through the captured step and through the eager one."""
+    from gophonic_b200.engine import Engine, StepError
+    eng = engines("B", dtype)
+    cfg, _ = plain_models["B"]
+    rng = np.random.default_rng(31)
+    prompts = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in (5, 40, 1, 17)]
+    source_host = rng.integers(0, cfg["vocab_size"], size=6).tolist()
+    source = torch.tensor(source_host, dtype=torch.int32, device=eng.device)
+    positions = [4, 0, 5, 2]
+    outs = []
+    for mode in ("host", "device"):
+        slots = [eng.new_sequence() for _ in prompts]
+        eng.step([(s, p) for s, p in zip(slots, prompts)])
+        if mode == "host":
+            out = eng.step([(s, [source_host[p]]) for s, p in zip(slots, positions)])
+        else:
+            out = eng.step_from(slots, source, positions)
+        outs.append(out.clone())
+        assert [eng.length(s) for s in slots] == [len(p) + 1 for p in prompts]
+        with pytest.raises(StepError, match="outside the source"):
+            eng.step_from(slots, source, [0, 1, 2, 6])
+        assert [eng.length(s) for s in slots] == [len(p) + 1 for p in prompts]
+        fetched = eng.fetch_tokens(source).wait()
+        assert fetched == source_host
+        for s in slots:
+            eng.end_sequence(s)
+    assert torch.equal(outs[0], outs[1])
+    eng.cache.check()
+
+
 def test_refused_steps_leave_the_cache_as_it_was(engines, plain_models):
     from gophonic_b200.cache import CacheFull
     from gophonic_b200.engine import StepError
