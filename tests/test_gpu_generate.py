@@ -151,3 +151,34 @@ def test_command_line(model_dirs, plain_models):
     bad = subprocess.run([sys.executable, "-m", "gophonic_b200", "-model", "/nonexistent", "1"], cwd=ROOT,
                          capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "gophonic_b200:" in bad.stderr
+
+
+def test_running_ahead_and_reading_every_token_first_give_the_same_replies(lanes, plain_models):
+    """Many requests of random lengths, budgets and stop tokens, greedy and sampled, more than a batch
+    holds: the loop that runs one step ahead (the engine's own) and the loop that reads every token
+    before the next step (the same engine behind a face without ``step_from``) reply alike, and the
+    cache is whole afterwards."""
+    import gophonic_b200 as g
+    from gophonic_b200.engine.generate import Generator
+    gen = lanes("A", g.FormatF32, batch=4)
+    cfg, _ = plain_models["A"]
+    rng = np.random.default_rng(77)
+    prompts = [rng.integers(0, cfg["vocab_size"], size=int(n)).tolist() for n in rng.integers(1, 60, size=23)]
+    options = [g.ChatOptions(MaxTokens=int(rng.integers(1, 30)), Temperature=float(rng.choice([0.0, 0.9])),
+                             TopK=int(rng.choice([0, 5])), Presence=float(rng.choice([0.0, 0.7])), Seed=int(rng.integers(0, 1000)))
+               for _ in prompts]
+    stop = [int(t) for t in rng.integers(0, cfg["vocab_size"], size=60)]   # a ninth of the vocabulary stops a reply
+
+    class ReadFirst:
+        """The engine without the calls that let the loop run ahead."""
+
+        def __init__(self, eng):
+            self.new_sequence, self.end_sequence, self.step, self.room = eng.new_sequence, eng.end_sequence, eng.step, eng.room
+
+    ahead = gen.Generate(prompts, options, stop_ids=stop)
+    assert gen.engine.cache.pages.held() == 0 and gen.engine.cache.slots.held() == 0
+    plain_loop = Generator(ReadFirst(gen.engine), gen.sampler, gen.batch, gen.context, stop).generate(prompts, options)
+    assert ahead == plain_loop
+    assert any(len(r) < o.MaxTokens for r, o in zip(ahead, options)), "some reply ended on a stop token"
+    gen.engine.cache.check()
+    assert gen.engine.cache.pages.held() == 0 and gen.engine.cache.slots.held() == 0
