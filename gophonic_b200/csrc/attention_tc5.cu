@@ -165,7 +165,8 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 
 __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
-                                                                   const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+                                                                   const __grid_constant__ CUtensorMap map_v, AttnParams p,
+                                                                   int by_kv_head) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
@@ -179,11 +180,21 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();  // the tile's extent comes from the step's metadata
     pdl_trigger();
-    // heads vary fastest and the longest tiles of all heads come first, so the SMs that finish a
-    // long tile early pick up the short ones (tiles of a causal prompt differ eightfold in work)
-    const int seq = blockIdx.z, head = blockIdx.x;
+    // The order in which CTAs start.  Short prompts: heads vary fastest and the longest tiles of all
+    // heads come first, so the SMs that finish a long tile early pick up the short ones (tiles of a
+    // causal prompt differ manyfold in work).  Long prompts, whose keys and values do not fit L2
+    // together: one kv head after the other (the query heads that share it side by side, longest
+    // tiles first), so that what runs together reads the same keys and values.
+    const int seq = blockIdx.z;
+    int head = blockIdx.x, qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+    if (by_kv_head) {
+        const int G = p.heads / p.kv_heads, tiles = (int)gridDim.y;
+        const int id = (int)blockIdx.x + (int)gridDim.x * (int)blockIdx.y;
+        const int per = G * tiles, rem = id % per;
+        head = (id / per) * G + rem % G;
+        qt = tiles - 1 - rem / G;
+    }
     const int q_len = p.seq_q_len[seq], kv_len = p.seq_kv_len[seq];
-    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int q0 = qt * (GROUPS * BQ);
     if (q0 >= q_len) return;  // the whole CTA leaves before anything is allocated
     const int past = kv_len - q_len;
@@ -573,7 +584,9 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (int rc = make_map(&map_v, p.v_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
     dim3 grid(p.heads, ceil_div(p.max_q_len, GROUPS * BQ), p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
-    cudaError_t e = launch_pdl(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p);
+    // keys and values of the longest prompt, all kv heads: more than 48 MB do not stay in L2 beside the rest
+    const int by_kv_head = (int64_t)p.max_q_len * p.kv_heads * (4 * HD) > ((int64_t)48 << 20) ? 1 : 0;
+    cudaError_t e = launch_pdl(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p, by_kv_head);
     if (e != cudaSuccess) GB_REFUSE("%s: launch failed: %s", who, cudaGetErrorString(e));
     return 0;
 }
