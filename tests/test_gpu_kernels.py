@@ -339,6 +339,28 @@ def test_attention_prompts_head_dim_128_both_tensor_core_kernels(ops, algo, head
     assert ops.tc5_status() == 0
 
 
+def test_attention_long_prompt_starts_its_ctas_kv_head_by_kv_head(ops):
+    """A prompt whose keys and values (all kv heads) pass 48 MB makes the tcgen05 kernel start its CTAs
+    one kv head after the other; the mma.sync kernel, which has no such order, must agree with it."""
+    heads, kvh, d, n = 32, 16, 128, 6200          # 6200 * 16 * 512 bytes = 50.8 MB
+    pages = (n + 63) // 64
+    k_plane, v_plane = paged(pages, kvh, d, torch.bfloat16, 5)
+    table = torch.randperm(pages, generator=torch.Generator().manual_seed(2)).to(torch.int32).reshape(1, pages).to(DEV)
+    q = rnd(n, heads * d, dtype=torch.bfloat16, seed=6)
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    outs = {}
+    for algo in ("prefill_tc5", "prefill_mma"):
+        out = torch.full((n, heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        used = ops.attention(q, out, k_plane, v_plane, table, 0, mk([0]), mk([0]), mk([n]), mk([n]), 1, n, heads, kvh, d,
+                             d ** -0.5, 0, 1, None, algo=algo)
+        assert used == algo
+        outs[algo] = out.float()
+    assert ops.tc5_status() == 0
+    assert torch.isfinite(outs["prefill_tc5"]).all()
+    err = (outs["prefill_tc5"] - outs["prefill_mma"]).abs().max() / outs["prefill_mma"].abs().max()
+    assert err < 1.2e-2, float(err)
+
+
 @pytest.mark.parametrize("dtype,algo", KINDS)
 @pytest.mark.parametrize("heads,kvh,d", GEOMS)
 @pytest.mark.parametrize("splits", [1, 3, 8])
