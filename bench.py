@@ -294,7 +294,25 @@ def probe(name):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / 3
     rate = work / (ms * 1e-3) / {"TFLOP/s": 1e12, "GB/s": 1e9}.get(unit, 1.0)
-    print(json.dumps({"probe": name, "ms": round(ms, 4), "rate": round(rate, 1), "unit": unit, "status": ops.tc5_status()}))
+    hbm_peak, tflops_peak, which = peaks()
+    line = {"probe": name, "ms": round(ms, 4), "rate": round(rate, 1), "unit": unit, "status": ops.tc5_status()}
+    if unit == "TFLOP/s":
+        line.update(frac=round(rate / tflops_peak, 4), of=f"{tflops_peak:.0f} TFLOP/s bf16 ({which})")
+    elif unit == "GB/s":
+        line.update(frac=round(rate / hbm_peak, 4), of=f"{hbm_peak:.0f} GB/s HBM ({which})")
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+KERNEL_PROBES = ("gemm_prefill", "gemm_prefill_swiglu", "attn_prefill", "gemm_decode_b8", "gemm_decode_b64", "attn_decode_b8",
+                 "attn_decode_b64")
+
+
+def profile():
+    """One line per hot kernel: its time on a workload of the benchmark's sizes, the bytes or flops it
+    has to move, and the fraction of the roofline that is."""
+    for name in KERNEL_PROBES:
+        probe(name)
     return 0
 
 
@@ -309,10 +327,13 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes (default: the benchmark's own, 8b)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length each sequence is filled to")
+    ap.add_argument("--profile", action="store_true", help="time each hot kernel alone and print its fraction of the roofline")
     ap.add_argument("--probe", default="", help="run one kernel on a small fixed workload (for profilers) and exit")
     args = ap.parse_args()
     if args.probe:
         return probe(args.probe)
+    if args.profile:
+        return profile()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "GetStream/gophonic is a Go module (no setup.py/pyproject; pip "
                           "refuses it), there is no Go toolchain here, and its GPU paths are Metal/WebGPU only"}))

@@ -332,6 +332,37 @@ def test_a_step_that_takes_its_tokens_from_the_device_equals_one_given_them(engi
     eng.cache.check()
 
 
+def test_warm_decode_steps_take_no_memory_from_the_device(engines, plain_models):
+    """Once a decode step of a given batch has run (its graph captured, the allocator's pools warm),
+    further steps and selections ask the device for no memory: no new segment, no growth of what is
+    reserved (internal/qwen3lm/weights_test.go:149-155 asserts the same of its warm step)."""
+    from gophonic_b200.sampling import DeviceSampler, Options
+    eng = engines("B", "bfloat16")
+    cfg, _ = plain_models["B"]
+    sampler = DeviceSampler(cfg["vocab_size"], 4, eng.device)
+    slots = [eng.new_sequence() for _ in range(3)]
+    for r in range(3):
+        sampler.start(r, Options(Temperature=0.8, TopK=20, Seed=r), r)
+    logits = eng.step([(s, [1, 2, 3, 4 + i]) for i, s in enumerate(slots)])
+    toks = sampler.select_device(logits, [0, 1, 2])
+    for _ in range(5):   # warm: capture, pools
+        logits = eng.step_from(slots, toks, [0, 1, 2])
+        toks = sampler.select_device(logits, [0, 1, 2])
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()
+    for _ in range(40):  # stays within one cache page per sequence
+        logits = eng.step_from(slots, toks, [0, 1, 2])
+        toks = sampler.select_device(logits, [0, 1, 2])
+        eng.fetch_tokens(toks).wait()
+    torch.cuda.synchronize()
+    after = torch.cuda.memory_stats()
+    for key in ("num_device_alloc", "segment.all.allocated", "reserved_bytes.all.current"):
+        if key in before:
+            assert after[key] == before[key], key
+    for s in slots:
+        eng.end_sequence(s)
+
+
 def test_refused_steps_leave_the_cache_as_it_was(engines, plain_models):
     from gophonic_b200.cache import CacheFull
     from gophonic_b200.engine import StepError
