@@ -25,7 +25,8 @@ def main(argv=None) -> int:
     ap.add_argument("-top-p", "--top-p", type=float, default=0.0, help="nucleus probability (0 or 1: off)")
     ap.add_argument("-presence", "--presence", type=float, default=0.0, help="presence penalty")
     ap.add_argument("-seed", "--seed", type=int, default=0, help="sampling seed")
-    ap.add_argument("-stop", "--stop", default="", help="comma-separated stop token ids")
+    ap.add_argument("-stop", "--stop", default=None,
+                    help="comma-separated stop token ids (default: the end-of-sequence ids the model folder names; '' for none)")
     ap.add_argument("-batch", "--batch", type=int, default=8, help="sequences that start together")
     ap.add_argument("-device", "--device", default="cuda:0")
     ap.add_argument("prompts", nargs="+", help="prompts as comma-separated token ids")
@@ -36,7 +37,7 @@ def main(argv=None) -> int:
     from .api import ChatOptions, Lane, Open, Options, TokensGenerator
     try:
         prompts = [[int(t) for t in p.replace(" ", "").split(",") if t] for p in args.prompts]
-        stops = [int(t) for t in args.stop.split(",") if t]
+        stops = None if args.stop is None else [int(t) for t in args.stop.split(",") if t]
     except ValueError as e:
         print(f"gophonic_b200: {e}", file=sys.stderr)
         return 2

@@ -153,10 +153,30 @@ def _is_model_dir(path: str) -> bool:
         return False
 
 
+def read_stop_ids(path: str) -> List[int]:
+    """The end-of-sequence token ids a model folder names in ``generation_config.json`` (one id or a
+    list), else in ``config.json``; none if neither says.  qwen3/chat.go:88-92 takes its stop tokens
+    from the tokenizer's added tokens; this library works on ids and reads the ids the folder gives."""
+    for name in ("generation_config.json", "config.json"):
+        try:
+            with open(os.path.join(path, name)) as fh:
+                eos = json.load(fh).get("eos_token_id")
+        except (OSError, ValueError):
+            continue
+        if isinstance(eos, bool) or eos is None:
+            continue
+        if isinstance(eos, int):
+            return [eos]
+        if isinstance(eos, list) and all(isinstance(t, int) and not isinstance(t, bool) for t in eos):
+            return list(eos)
+    return []
+
+
 class TokenGenerator:
     """Lane "tokens.Generator": replies to prompts given as token ids."""
 
-    def __init__(self, model, opts: Options):
+    def __init__(self, model, opts: Options, stop_ids: Sequence[int] = ()):
+        self.stop_ids = list(stop_ids)  # the folder's own end-of-sequence ids: the default of Generate
         from .engine.generate import Generator
         from .engine.step import Engine
         from .sampling.sampler import DeviceSampler
@@ -169,10 +189,12 @@ class TokenGenerator:
         self.context = min(context, self.engine.capacity)
         self.batch = opts.Batch
 
-    def Generate(self, prompts: Sequence[Sequence[int]], options=None, stop_ids: Sequence[int] = (),
+    def Generate(self, prompts: Sequence[Sequence[int]], options=None, stop_ids: Optional[Sequence[int]] = None,
                  on_token=None) -> List[List[int]]:
+        """Replies to ``prompts`` (lists of token ids), in order.  ``stop_ids``: the token ids that
+        end a reply (not part of it); None takes the ids the model folder names, () none at all."""
         from .engine.generate import Generator
-        g = Generator(self.engine, self.sampler, self.batch, self.context, stop_ids)
+        g = Generator(self.engine, self.sampler, self.batch, self.context, self.stop_ids if stop_ids is None else stop_ids)
         out = g.generate(prompts, options, on_token)
         self.engine.check_kernels()
         self.stats = g.stats
@@ -188,7 +210,7 @@ def _open_dir(path: str, opts: Options) -> OpenedModel:
     model = Model.from_dir(path, dtype=mode, device=opts.Device)
     m = OpenedModel(model.spec.architecture, path)
     m.model = model
-    return Provide(m, TokensGenerator, lambda: TokenGenerator(model, opts))
+    return Provide(m, TokensGenerator, lambda: TokenGenerator(model, opts, read_stop_ids(path)))
 
 
 Register(Format(Name="model-folder", Match=_is_model_dir, Open=_open_dir, Provides=(TokensGenerator,)))

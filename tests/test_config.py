@@ -112,3 +112,17 @@ def test_part_registry_errors_and_replacement():
         pass
     registry.register_mixer("dummy-for-test", Dummy)
     assert registry.part_class("mixer", "dummy-for-test") is Dummy
+
+
+def test_stop_ids_come_from_the_model_folder(tmp_path):
+    import json
+    from gophonic_b200.api import read_stop_ids
+    d = tmp_path / "m"
+    d.mkdir()
+    assert read_stop_ids(str(d)) == []
+    (d / "config.json").write_text(json.dumps({"eos_token_id": 7}))
+    assert read_stop_ids(str(d)) == [7]
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": [151645, 151643]}))
+    assert read_stop_ids(str(d)) == [151645, 151643]          # the generation config wins
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    assert read_stop_ids(str(d)) == [7]                         # what is no id or list of ids is passed over
