@@ -144,7 +144,8 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) 
 def gemm_add_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     """Whether ``gemm_add`` takes this product: a prompt-sized bfloat16 product into a float32 ``out``."""
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.float32 and a.dim() == 2
-            and a.shape[0] >= TC5_PAIR_MIN_ROWS and w.is_contiguous() and tc5_accepts(a, w, out))
+            and a.shape[0] >= TC5_PAIR_MIN_ROWS and w.is_contiguous() and tc5_accepts(a, w, out)
+            and out.stride(0) % 4 == 0 and out.data_ptr() % 16 == 0)
 
 
 def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
