@@ -49,6 +49,11 @@ def tiny_configs():
         "D": Qwen3Config(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                          head_dim=128, intermediate_size=520, vocab_size=2000, max_position_embeddings=1024,
                          rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False),
+        # widths whose bfloat16 rows are not 16-byte aligned (84, 100): the tensor-core kernels refuse
+        # them and every product of the bfloat16 model runs on the CUDA-core kernel instead
+        "E": Qwen3Config(hidden_size=84, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3,
+                         head_dim=16, intermediate_size=100, vocab_size=257, max_position_embeddings=600,
+                         rms_norm_eps=1e-5, rope_theta=20000.0, tie_word_embeddings=True),
     }
 
 

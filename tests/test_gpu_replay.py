@@ -58,11 +58,12 @@ def references(plain_models):
     return get
 
 
-LENGTHS = {"A": [1, 5, 17, 70, 131], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 129], "D": [1, 64, 65, 130, 200, 300, 520]}
+LENGTHS = {"A": [1, 5, 17, 70, 131], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 129], "D": [1, 64, 65, 130, 200, 300, 520],
+           "E": [1, 9, 70, 300]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "A32"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "A32"])
 def test_each_request_alone_and_whole(engines, references, plain_models, name, dtype):
     eng = engines(name, dtype)
     cfg, _ = plain_models[name]
@@ -80,7 +81,7 @@ def test_each_request_alone_and_whole(engines, references, plain_models, name, d
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_last_32_tokens_one_by_one(engines, references, plain_models, name, dtype):
     eng = engines(name, dtype)
     cfg, _ = plain_models[name]
