@@ -179,6 +179,41 @@ def time_entry_point(model, batch, steps, warmup, context, torch):
     return out
 
 
+def run_mixed_batch(model, torch, requests=16, shortest=64, longest=2048, new_tokens=256):
+    """A batch of prompts of unequal lengths (seeded, uniform in [shortest, longest]) that start
+    together and then decode ``new_tokens`` tokens each, through the public entry point with host
+    token ids in and out; wall clock, once untimed and once timed."""
+    import numpy as np
+    import gophonic_b200 as gp
+    from gophonic_b200.api import TokenGenerator
+    gen = TokenGenerator(model, gp.Options(Format=gp.FormatBF16, CacheTokens=requests * (longest + new_tokens), Batch=requests))
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(shortest, longest + 1, size=requests).tolist()
+    prompts = [rng.integers(0, model.spec.vocab, size=n).tolist() for n in lengths]
+    out = {}
+    for timed in (False, True):
+        marks = {}
+
+        def on_token(i, token):
+            if "first" not in marks:
+                marks["first"] = time.perf_counter()
+
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        replies = gen.Generate(prompts, gp.ChatOptions(MaxTokens=new_tokens, Temperature=0.0), on_token=on_token)
+        t1 = time.perf_counter()
+        assert all(len(r) == new_tokens for r in replies)
+        if timed:
+            out = {"workload": f"{requests} prompts of {shortest}..{longest} tokens that start together, then {new_tokens} tokens each",
+                   "prompt_tokens": int(sum(lengths)), "prefill_ms": round((marks["first"] - t0) * 1e3, 2),
+                   "prefill_tok_s": round(sum(lengths) / (marks["first"] - t0), 1),
+                   "decode_steps": new_tokens - 1, "decode_ms_per_step": round((t1 - marks["first"]) * 1e3 / (new_tokens - 1), 4),
+                   "decode_tok_s": round(requests * (new_tokens - 1) / (t1 - marks["first"]), 1),
+                   "total_s": round(t1 - t0, 4)}
+    gen.Close()
+    return out
+
+
 def time_prefill(engine, tokens, iters, warmup, torch):
     import numpy as np
     rng = np.random.default_rng(1)
@@ -327,6 +362,9 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes (default: the benchmark's own, 8b)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length each sequence is filled to")
+    ap.add_argument("--mixed", action="store_true",
+                    help="instead of the headline run: 16 prompts of 64 to 2048 tokens that start together, then 256 tokens each, "
+                         "through the entry point (a further point, with --model)")
     ap.add_argument("--profile", action="store_true", help="time each hot kernel alone and print its fraction of the roofline")
     ap.add_argument("--probe", default="", help="run one kernel on a small fixed workload (for profilers) and exit")
     args = ap.parse_args()
@@ -359,6 +397,12 @@ def main():
                       tie_word_embeddings=sz["tied"])
     hbm_peak, tflops_peak, which = peaks()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    if args.mixed:
+        line = run_mixed_batch(model, torch)
+        line.update({"model": f"Qwen3-{args.model.upper()}-shaped", "layers": layers, "layers_full": full_layers, "dtype": "bf16",
+                     "data": "synthetic: seeded random weights and token ids", "timing": "wall clock around the entry point's call"})
+        print(json.dumps(line))
+        return 0
     max_batch = args.batch if args.no_points else max(args.batch, 64)
     engine = Engine(model, max_tokens=max_batch * context, max_slots=max_batch, max_seq_tokens=context)
     fill_cache_random(engine, torch)
