@@ -375,8 +375,10 @@ class Engine:
                     pieces.append((slot, list(toks[a - starts[i]:b - starts[i]]), self.cache.length(slot) + a - starts[i]))
             local = sorted({row for row in want_rows if lo <= row < hi})
             logits = self._pass(pieces, [row - lo for row in local])
-            for j, row in enumerate(local):
-                for k in order[row]:
-                    result[k].copy_(logits[j])
+            ks = [k for row in local for k in order[row]]
+            if ks:
+                js = [j for j, row in enumerate(local) for _ in order[row]]
+                result.index_copy_(0, torch.tensor(ks, dtype=torch.int64, device=self.device),
+                                   logits.index_select(0, torch.tensor(js, dtype=torch.int64, device=self.device)))
             lo = hi
         return result
