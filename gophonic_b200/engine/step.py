@@ -64,11 +64,39 @@ class StepBatch:
         return splits, self._scratch[key]
 
 
-def choose_splits(units: int, max_kv_len: int, sm_count: int = 148) -> int:
-    """``units`` = (sequence, kv head) pairs, each one CTA per split."""
-    by_len = max(1, max_kv_len // 256)
-    by_occupancy = max(1, (2 * sm_count) // max(1, units))
-    return int(max(1, min(by_len, by_occupancy, 32)))
+def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: int = 32768) -> int:
+    """How many pieces single-token attention cuts each sequence's keys into.  ``units`` =
+    (sequence, kv head) pairs, each one CTA per piece; ``page_bytes`` = keys and values of one kv
+    head for one page of 64 tokens.
+
+    The choice minimises a small model of the kernel's time that was fitted to measurements at 1
+    to 64 sequences of 4096 keys: two CTAs fit on an SM and run in waves; a wave takes the longer
+    of its bytes at the memory bandwidth and of one CTA's own pace (a little over a microsecond a page),
+    so a thin last wave costs as much as a full one unless its CTAs are short; cutting the keys
+    costs the merge kernel.  A piece keeps at least 256 keys.
+    """
+    units = max(1, units)
+    pages = max(1, (max_kv_len + 63) // 64)
+    most = max(1, min(32, max_kv_len // 256))
+    slots = 2 * sm_count
+    bytes_per_us = 6.0e6
+    page_us = 0.575 + 0.575 * page_bytes / 32768.0
+    if units > 2 * slots:
+        return 1  # more than two full waves uncut: what a thin last wave costs is small, and nothing here was measured
+    best, best_t = 1, None
+    for s in range(1, most + 1):
+        p = (pages + s - 1) // s
+        ctas = units * s
+        full, rest = divmod(ctas, slots)
+        pace = p * page_us + 3.0
+        t = full * max(slots * p * page_bytes / bytes_per_us, pace)
+        if rest:
+            t += max(rest * p * page_bytes / bytes_per_us, pace)
+        if s > 1:
+            t += 5.0 + 0.15 * s
+        if best_t is None or t < 0.98 * best_t:
+            best, best_t = s, t
+    return best
 
 
 class HostStager:

@@ -148,3 +148,25 @@ def test_random_walk_keeps_invariants():
         c.free_slot(s)
     c.check()
     assert c.pages.held() == 0 and c.slots.held() == 0
+
+
+def test_key_splits_of_single_token_attention():
+    """The choice of how many pieces a sequence's keys are cut into: short contexts are not cut, a
+    piece keeps at least 256 keys, few sequences are cut until every SM has work, and a batch
+    that fills the machine a little more than once is cut so that its last wave is not thin."""
+    from gophonic_b200.engine import choose_splits
+    for units in (1, 8, 64, 300, 512, 4000):
+        assert choose_splits(units, 1) == 1
+        assert choose_splits(units, 255) == 1
+        for kv_len in (256, 1000, 4096, 32768):
+            s = choose_splits(units, kv_len)
+            assert 1 <= s <= max(1, min(32, kv_len // 256))
+    # the cases the model was fitted to (kv heads 8, 4096 keys, 148 SMs)
+    assert choose_splits(8, 4096) == 16          # one sequence
+    assert choose_splits(64, 4096) == 4          # eight: 256 CTAs for 296 places
+    assert choose_splits(96, 4096) == 3
+    assert choose_splits(128, 4096) == 2
+    assert choose_splits(256, 4096) == 1         # 32 sequences: one wave, nearly full
+    assert choose_splits(384, 4096) == 3         # 48: uncut, 88 CTAs would run alone after the first 296
+    assert choose_splits(512, 4096) == 1         # 64: two waves, the second well filled
+    assert choose_splits(5000, 4096) == 1
