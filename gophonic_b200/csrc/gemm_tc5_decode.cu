@@ -1,12 +1,13 @@
-// Y[M, N] = X[M, K] * W[N, K]^T for a batch of 9 to 64 rows on tcgen05: the decode-step product
-// when there are too many rows for the fragment-streaming kernel to stay bound by memory.
+// Y[M, N] = X[M, K] * W[N, K]^T for 9 to 256 rows on tcgen05: the product of a decode step, or of
+// a short prompt, when there are too many rows for the fragment-streaming kernel and too few for
+// the tiled kernels to give every SM a share of the weights.
 //
 // The weights take the M side of the instruction: a CTA owns 128 rows of W and a slice of K, and
-// computes Y^T[128, batch] with UMMA M = 128, N = 16 / 32 / 64 (the batch rounded up; TMA fills
-// the missing rows of X with zeros).  Per K step of 64 a stage holds 16 KB of W from HBM and at
-// most 8 KB of X from L2, four stages deep, two CTAs to an SM, so every SM keeps tens of KB of
-// weights in flight.  K is cut into slices so that about two CTAs per SM exist even for narrow
-// outputs.  The CTAs that share a tile (1, 2, 4 or 8 slices of K) form a thread-block cluster:
+// computes Y^T[128, batch] with UMMA M = 128, N = 16 / 32 / 64 / 128 / 256 (the batch rounded up;
+// TMA fills the missing rows of X with zeros).  Per K step of 64 a stage holds 16 KB of W from HBM
+// and 2 to 32 KB of X from L2; up to 64 rows four stages deep, above that three; two CTAs to an SM
+// (one at 256 columns), so every SM keeps tens of KB of weights in flight.  K is cut into slices so
+// that about that many CTAs exist even for narrow outputs.  The CTAs that share a tile (1, 2, 4 or 8 slices of K) form a thread-block cluster:
 // each leaves its partial tile in its own shared memory, and after a cluster barrier each CTA adds
 // the slices, in slice order, for its share of the tile's rows, reading the other CTAs' shared
 // memory directly (distributed shared memory).  No scratch in global memory, and the sum does not
@@ -22,7 +23,7 @@ namespace {
 
 __device__ int g_status;
 
-constexpr int BMW = 128, BK = 64, STAGES = 4, THREADS = 192;
+constexpr int BMW = 128, BK = 64, THREADS = 192;
 constexpr int W_BYTES = BMW * BK * 2;
 
 __device__ __forceinline__ float silu_f(float x) {
@@ -42,7 +43,7 @@ __device__ __forceinline__ void store_out(TC* __restrict__ Y, int64_t ldy, int b
     }
 }
 
-template <typename TC, int NB>  // NB = batch columns of the instruction: 16, 32 or 64
+template <typename TC, int NB, int STAGES>  // NB = batch columns of the instruction: 16 to 256; STAGES deep
 __global__ void __launch_bounds__(THREADS) gemm_tc5_decode_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x, TC* __restrict__ Y,
                                                                  int M, int N, int K, int64_t ldy, int splits, int kb_per_split,
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_decode_kernel(const __grid_c
 
 constexpr int MAX_TILES = 8192;
 
-template <typename TC, int NB>
+template <typename TC, int NB, int STAGES>
 int launch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldy, int epi, int splits,
            cudaStream_t stream) {
     constexpr int X_BYTES = NB * BK * 2;
@@ -214,7 +215,7 @@ int launch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t l
     if (part > smem) smem = part;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_decode_kernel<TC, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_decode_kernel<TC, NB, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) GB_REFUSE("gemm_tc5_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -226,7 +227,7 @@ int launch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t l
     while (splits > 1 && KB < splits) splits >>= 1;
     const int kb_per_split = ceil_div(KB, splits);
     if (tiles > MAX_TILES) GB_REFUSE("gemm_tc5_decode: N = %d exceeds %d tiles", N, MAX_TILES);
-    cudaError_t e = launch_pdl_cluster(gemm_tc5_decode_kernel<TC, NB>, dim3(tiles, splits), dim3(THREADS), (size_t)smem, stream, 1,
+    cudaError_t e = launch_pdl_cluster(gemm_tc5_decode_kernel<TC, NB, STAGES>, dim3(tiles, splits), dim3(THREADS), (size_t)smem, stream, 1,
                                        (unsigned)splits, map_w, map_x, (TC*)Y, M, N, K, ldy, splits, kb_per_split, epi);
     if (e != cudaSuccess) GB_REFUSE("gemm_tc5_decode: launch failed: %s", cudaGetErrorString(e));
     return 0;
@@ -235,9 +236,11 @@ int launch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t l
 template <typename TC>
 int dispatch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldy, int epi, int splits,
              cudaStream_t stream) {
-    if (M <= 16) return launch<TC, 16>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
-    if (M <= 32) return launch<TC, 32>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
-    return launch<TC, 64>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    if (M <= 16) return launch<TC, 16, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    if (M <= 32) return launch<TC, 32, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    if (M <= 64) return launch<TC, 64, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    if (M <= 128) return launch<TC, 128, 3>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
+    return launch<TC, 256, 3>(X, W, Y, M, N, K, ldx, ldy, epi, splits, stream);
 }
 
 }  // namespace
@@ -254,7 +257,8 @@ GB_API int gb_gemm_tc5_decode_splits(int M, int N, int K, int sms) {
     const int tiles = ceil_div(N, BMW), KB = ceil_div(K, BK);
     if (sms <= 0) sms = 1;
     if (M > 16) {
-        int want = (2 * sms) / (tiles > 0 ? tiles : 1);
+        const int per_sm = M > 128 ? 1 : 2;  // CTAs that fit on an SM with the operand stages of this many rows
+        int want = (per_sm * sms) / (tiles > 0 ? tiles : 1);
         if (want > KB / 8) want = KB / 8;
         int s = 1;
         while (s * 2 <= want && s < 8) s *= 2;
@@ -279,7 +283,7 @@ GB_API int gb_gemm_tc5_decode_splits(int M, int N, int K, int sms) {
 GB_API int gb_gemm_tc5_decode(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
                               int epi, int splits, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 64) GB_REFUSE("gemm_tc5_decode: %d rows; this kernel takes at most 64", M);
+    if (M > 256) GB_REFUSE("gemm_tc5_decode: %d rows; this kernel takes at most 256", M);
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5_decode: K = %d must be a positive multiple of 8", K);
     if ((ldx & 7) || ldx < K) GB_REFUSE("gemm_tc5_decode: row stride %lld of X must be a multiple of 8 and at least K", (long long)ldx);
     if (epi == 0 && ldy < N) GB_REFUSE("gemm_tc5_decode: row stride %lld of Y is shorter than N = %d", (long long)ldy, N);

@@ -214,9 +214,10 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto") -> str:
     """out = a @ w^T, choosing the kernel by operand types and sizes.  Returns the kernel's name.
 
-    bfloat16 activations with bfloat16 weights go to the tensor-core kernels: up to 8 rows the
-    fragment-streaming kernel, up to 64 the tcgen05 decode kernel, 65 to 127 mma.sync tiles, from 128
-    the tiled tcgen05 kernel and from 192 the one that pairs two SMs on a tile.  Everything else,
+    bfloat16 activations with bfloat16 weights go to the tensor-core kernels (``gemm_algo``): up to
+    8 rows the fragment-streaming kernel, up to 128 (256 for narrow outputs with a long K) the
+    tcgen05 decode kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs
+    two SMs on a tile; mma.sync tiles only when asked for by name.  Everything else,
     and operands whose rows are not 16-byte aligned, goes to the fp32 CUDA-core kernel.  float32
     operands never touch a tensor core.
     """
@@ -238,16 +239,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
         gemm_simt(a, w, out)
         return "simt"
     if algo == "auto":
-        if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT:
-            algo = "skinny"        # weights streamed straight into mma.sync fragments
-        elif M <= 64:
-            algo = "tc5_decode"    # tcgen05, weights on the M side, K slices across a cluster
-        elif M >= TC5_PAIR_MIN_ROWS:
-            algo = "tc5_pair"      # tcgen05 on pairs of SMs, 256 x 256 tiles
-        elif M >= 128:
-            algo = "tc5"           # tcgen05, 128 x 256 tiles
-        else:
-            algo = "mma"           # mma.sync tiles
+        algo = gemm_algo(M, N, K)
     if algo == "skinny":
         _check(_lib.gb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                    c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
@@ -269,6 +261,26 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     return algo
 
 
+def gemm_algo(M: int, N: int, K: int) -> str:
+    """The tensor-core kernel ``gemm`` picks for aligned bfloat16 operands of these sizes (measured
+    on the four products of an 8B layer, 1 to 2048 rows)."""
+    if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT:
+        return "skinny"            # weights streamed straight into mma.sync fragments
+    if M <= 64:
+        return "tc5_decode"        # tcgen05, weights on the M side, K slices across a cluster
+    if M <= TC5_DECODE_MAX_ROWS // 2:
+        # up to 128 rows the step is still bound by reading the weights: the decode kernel gives
+        # every SM a share of them, the tiled kernel only where the output is wide enough for that
+        return "tc5_decode" if (N + 127) // 128 < 148 else "tc5"
+    if M <= TC5_DECODE_MAX_ROWS and (N + 255) // 256 <= 16 and K >= 8192:
+        return "tc5_decode"        # a narrow output with a long K: too few tiles for the tiled kernels
+    if M >= TC5_PAIR_MIN_ROWS:
+        return "tc5_pair"          # tcgen05 on pairs of SMs, 256 x 256 tiles
+    return "tc5"                   # tcgen05, 128 x 256 tiles
+
+
+# rows up to which the tcgen05 decode kernel takes a product (its batch side is one instruction wide)
+TC5_DECODE_MAX_ROWS = 256
 # rows from which the tcgen05 kernel that pairs two SMs on tiles of 256 x 256 is used
 TC5_PAIR_MIN_ROWS = 192
 # rows up to which the fragment-streaming kernel is used for decode; above it (to 64) the tcgen05

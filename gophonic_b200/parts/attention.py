@@ -71,7 +71,7 @@ class Attention(Mixer):
     def adds_in_place(self, rows: int) -> bool:
         ops = self.rt.ops
         return (self.o.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.q_dim % 8 == 0 and self.spec.hidden % 4 == 0
-                and rows >= ops.TC5_PAIR_MIN_ROWS)
+                and ops.gemm_algo(rows, self.spec.hidden, self.q_dim) == "tc5_pair")
 
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
         self.rt.ops.gemm_add(self._context(batch, x, cache), self.o, h)

@@ -46,7 +46,7 @@ class SwiGLU(FeedForward):
     def adds_in_place(self, rows: int) -> bool:
         ops = self.rt.ops
         return (self.down.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.spec.intermediate % 8 == 0 and self.spec.hidden % 4 == 0
-                and rows >= ops.TC5_PAIR_MIN_ROWS)
+                and ops.gemm_algo(rows, self.spec.hidden, self.spec.intermediate) == "tc5_pair")
 
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor) -> None:
         self.rt.ops.gemm_add(self._activation(x), self.down, h)

@@ -137,12 +137,13 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
 
 
 @pytest.mark.parametrize("algo", ["skinny", "mma", "tc5", "tc5_pair", "tc5_decode"])
-@pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (300, 1000, 512), (2048, 512, 1024)])
+@pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (100, 1536, 2048), (128, 200, 8200), (256, 4096, 520),
+                                            (300, 1000, 512), (2048, 512, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
     out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    if algo in ("skinny", "tc5_decode") and M > 64:
+    if (algo == "skinny" and M > 64) or (algo == "tc5_decode" and M > ops.TC5_DECODE_MAX_ROWS):
         with pytest.raises(ops.KernelError):
             ops.gemm(a, w, out, algo=algo)
         return
