@@ -73,7 +73,8 @@ def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: 
     to 64 sequences of 4096 keys: two CTAs fit on an SM and run in waves; a wave takes the longer
     of its bytes at the memory bandwidth and of one CTA's own pace (a little over a microsecond a page),
     so a thin last wave costs as much as a full one unless its CTAs are short; cutting the keys
-    costs the merge kernel.  A piece keeps at least 256 keys.
+    costs the merge kernel and the traffic of the partial results.  A piece keeps at least 256
+    keys.
     """
     units = max(1, units)
     pages = max(1, (max_kv_len + 63) // 64)
@@ -81,8 +82,10 @@ def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: 
     slots = 2 * sm_count
     bytes_per_us = 6.0e6
     page_us = 0.575 + 0.575 * page_bytes / 32768.0
-    if units > 2 * slots:
-        return 1  # more than two full waves uncut: what a thin last wave costs is small, and nothing here was measured
+    if 4 * units > 9 * slots:
+        # more than two and a quarter waves uncut: the CTAs no longer run in step and a thin last
+        # wave costs little (112 sequences x 8 kv heads ran 2 % faster uncut than in 4 or 8 pieces)
+        return 1
     best, best_t = 1, None
     for s in range(1, most + 1):
         p = (pages + s - 1) // s
@@ -93,8 +96,10 @@ def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: 
         if rest:
             t += max(rest * p * page_bytes / bytes_per_us, pace)
         if s > 1:
-            t += 5.0 + 0.15 * s
-        if best_t is None or t < 0.98 * best_t:
+            # the merge kernel, and the partial results (about four heads a unit, 130 floats each)
+            # written and read back
+            t += 5.0 + 0.15 * s + units * s * 4 * 1040 / 3.0e6
+        if best_t is None or t < 0.99 * best_t:
             best, best_t = s, t
     return best
 
@@ -201,7 +206,7 @@ class Engine:
 
     def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
                  max_seq_tokens: Optional[int] = None, max_rows_per_pass: int = 16384, use_graphs: bool = True,
-                 max_graph_batch: int = 64):
+                 max_graph_batch: int = 128):
         self.model = model
         self.device = model.rt.device
         self.cache: Cache = model.new_cache(max_tokens, max_slots, max_seq_tokens)

@@ -169,4 +169,6 @@ def test_key_splits_of_single_token_attention():
     assert choose_splits(256, 4096) == 1         # 32 sequences: one wave, nearly full
     assert choose_splits(384, 4096) == 3         # 48: uncut, 88 CTAs would run alone after the first 296
     assert choose_splits(512, 4096) == 1         # 64: two waves, the second well filled
+    assert choose_splits(640, 4096) in (3, 4)    # 80: two full waves and 48 CTAs
+    assert choose_splits(896, 4096) == 1         # 112: three waves and more are left uncut
     assert choose_splits(5000, 4096) == 1
