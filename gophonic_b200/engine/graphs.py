@@ -61,8 +61,8 @@ class DecodeGraphs:
         self.graphs: Dict[Tuple[int, int], DecodeGraph] = {}
         self.pool = None
 
-    def get(self, nseq: int, max_kv_len: int, kv_heads_hint: int) -> DecodeGraph:
-        splits = choose_splits(nseq * kv_heads_hint, max_kv_len, self.engine.sm_count)
+    def get(self, nseq: int, max_kv_len: int, kv_heads_hint: int, page_bytes_hint: int = 32768) -> DecodeGraph:
+        splits = choose_splits(nseq * kv_heads_hint, max_kv_len, self.engine.sm_count, page_bytes_hint)
         key = (nseq, splits)
         g = self.graphs.get(key)
         if g is None:

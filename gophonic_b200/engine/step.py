@@ -47,14 +47,14 @@ class StepBatch:
     fixed_splits: Optional[int] = None
     _scratch: Dict[Tuple[int, int, int], torch.Tensor] = field(default_factory=dict)
 
-    def decode_splits(self, heads: int, kv_heads: int, head_dim: int) -> Tuple[int, Optional[torch.Tensor]]:
+    def decode_splits(self, heads: int, kv_heads: int, head_dim: int, elem_bytes: int = 2) -> Tuple[int, Optional[torch.Tensor]]:
         """How many pieces single-token attention cuts each sequence's keys into, and the scratch
         the pieces are merged through.  Few sequences with long contexts are cut so that every SM
         has work; many sequences are not cut."""
         if self.fixed_splits is not None:
             splits = self.fixed_splits
         else:
-            splits = choose_splits(self.nseq * kv_heads, self.max_kv_len, self.sm_count)
+            splits = choose_splits(self.nseq * kv_heads, self.max_kv_len, self.sm_count, 2 * 64 * head_dim * elem_bytes)
         if splits <= 1:
             return 1, None
         key = (heads, head_dim, splits)
@@ -223,7 +223,10 @@ class Engine:
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self, max_graph_batch)
         # kv heads of the widest attention group: how many CTAs a sequence gives single-token attention
-        self._kv_heads_hint = max([g["kv_heads"] for g in self.cache.groups() if g["kind"] == "kv"] or [1])
+        kv_groups = [g for g in self.cache.groups() if g["kind"] == "kv"]
+        self._kv_heads_hint = max([g["kv_heads"] for g in kv_groups] or [1])
+        # keys and values of one kv head for one page of 64 tokens, in the widest group
+        self._page_bytes_hint = max([g["bytes_per_token"] // (len(g["planes"]) * g["kv_heads"]) * 64 for g in kv_groups] or [32768])
 
     # ---- slots ---------------------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -359,7 +362,7 @@ class Engine:
         """One token each, every row wanted: replay the captured step."""
         n = len(entries)
         firsts = [self.cache.length(slot) for slot, _ in entries]
-        g = self.graphs.get(n, max(firsts) + 1, self._kv_heads_hint)
+        g = self.graphs.get(n, max(firsts) + 1, self._kv_heads_hint, self._page_bytes_hint)
         if g.logits is None:
             # the capture runs the step's kernels on the graph's own input buffer: fill it first
             self._fill_graph_meta(g, entries, firsts)

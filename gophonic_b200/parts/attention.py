@@ -93,7 +93,7 @@ class Attention(Mixer):
         ctx = torch.empty((rows, self.q_dim), dtype=x.dtype, device=x.device)
         splits, scratch = 1, None
         if batch.max_q_len == 1:
-            splits, scratch = batch.decode_splits(s.heads, s.kv_heads, s.head_dim)
+            splits, scratch = batch.decode_splits(s.heads, s.kv_heads, s.head_dim, cache.k.element_size())
         ops.attention(qkv[:, :self.q_dim], ctx, cache.k, cache.v, cache.block_table, cache.ring_pages,
                       batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len, batch.nseq,
                       batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),
