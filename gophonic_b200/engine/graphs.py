@@ -10,6 +10,8 @@ replayed step gives the eager step's logits bit for bit.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -19,7 +21,10 @@ from .step import StepBatch, choose_splits
 
 class DecodeGraph:
     def __init__(self, engine, nseq: int, splits: int, pool):
-        self.engine = engine
+        # the engine owns its graphs; a strong reference back would make a cycle, and an engine
+        # dropped by its user would then be freed by the collector at some later time, perhaps in
+        # the middle of another engine's capture, where freeing device memory is an error
+        self._engine = weakref.ref(engine)
         self.nseq = nseq
         dev = engine.device
         # ids | row_pos | row_seq | seq_slot | q_start | q_len | kv_len | want rows
@@ -36,6 +41,10 @@ class DecodeGraph:
         self.pool = pool
         self.kernels = 0
 
+    @property
+    def engine(self):
+        return self._engine()
+
     def capture(self) -> None:
         eng = self.engine
         ops = eng.model.rt.ops
@@ -43,8 +52,17 @@ class DecodeGraph:
         eng.model.forward(self.batch, eng.cache, self.want)
         torch.cuda.synchronize()
         before = ops.launches
-        with torch.cuda.graph(self.graph, pool=self.pool):
-            self.logits = eng.model.forward(self.batch, eng.cache, self.want)
+        # Nothing may be freed on the device while the stream captures: collect what is garbage
+        # now, and keep the collector from running until the capture has ended.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=self.pool):
+                self.logits = eng.model.forward(self.batch, eng.cache, self.want)
+        finally:
+            if collecting:
+                gc.enable()
         self.kernels = ops.launches - before
         ops.launches = before  # captured, not run
 
@@ -56,10 +74,14 @@ class DecodeGraph:
 
 class DecodeGraphs:
     def __init__(self, engine, max_batch: int = 64):
-        self.engine = engine
+        self._engine = weakref.ref(engine)
         self.max_batch = max_batch
         self.graphs: Dict[Tuple[int, int], DecodeGraph] = {}
         self.pool = None
+
+    @property
+    def engine(self):
+        return self._engine()
 
     def get(self, nseq: int, max_kv_len: int, kv_heads_hint: int, page_bytes_hint: int = 32768) -> DecodeGraph:
         splits = choose_splits(nseq * kv_heads_hint, max_kv_len, self.engine.sm_count, page_bytes_hint)

@@ -419,3 +419,89 @@ def test_trace_run_program(model_dirs, references, plain_models, tmp_path, dtype
     assert not (out / "2.f32").exists()
     assert rel_err(load(3), ra[32:33]) < TOL[dtype]
     assert rel_err(load(4), rc[[0, 69]]) < TOL[dtype]
+
+
+def test_an_engine_dropped_earlier_does_not_disturb_a_later_capture(model_dirs):
+    """An engine that captured a step and was dropped must be gone at once, not whenever the
+    collector runs: were it freed in the middle of a later engine's capture, the release of its
+    device memory would invalidate that capture.  The collector is run here inside the second
+    engine's capture on purpose."""
+    import gc
+    import weakref
+    from gophonic_b200.engine import Engine, Model
+    first = Engine(Model.from_dir(model_dirs["B"], dtype="bfloat16"), max_tokens=512)
+    slot = first.new_sequence()
+    first.step([(slot, [1, 2, 3])])
+    first.step([(slot, [4])])          # captured
+    gone = weakref.ref(first)
+    del first
+    assert gone() is None, "the engine is kept alive by a reference cycle"
+
+    second = Engine(Model.from_dir(model_dirs["B"], dtype="bfloat16"), max_tokens=512)
+    slot = second.new_sequence()
+    want = second.step([(slot, [1, 2, 3, 4])], [[3]]).cpu()
+    second.end_sequence(slot)
+    slot = second.new_sequence()
+    second.step([(slot, [1, 2, 3])])
+    forward = second.model.forward
+
+    def collecting_forward(*args):
+        gc.collect()
+        return forward(*args)
+    second.model.forward = collecting_forward
+    got = second.step([(slot, [4])]).cpu()   # the capture happens in this call
+    assert torch.equal(got, want) or float((got - want).abs().max() / want.abs().max()) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("trial", range(12))
+def test_random_configurations_and_plans(trial, tmp_path):
+    """Seeded random sizes (head sizes 16..128, one to four kv heads, groups of one to eight,
+    widths and vocabularies of every kind) and random plans: a batch of unequal prompts, then one
+    token each with early ends, twice over so that slots and pages are used again; both dtypes
+    against the plain implementation."""
+    from gophonic_b200.config import Qwen3Config
+    from gophonic_b200.engine import Engine, Model
+    from gophonic_b200.weights import InitScales, write_random_model
+    rng = np.random.default_rng(1000 + trial)
+    kvh = int(rng.choice([1, 2, 3, 4]))
+    cfg = Qwen3Config(hidden_size=int(rng.choice([40, 64, 72, 84, 96, 128, 136, 200, 256])),
+                      num_hidden_layers=int(rng.choice([1, 2, 3])),
+                      num_attention_heads=kvh * int(rng.choice([1, 2, 3, 4, 5, 8])), num_key_value_heads=kvh,
+                      head_dim=int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128])),
+                      intermediate_size=int(rng.choice([24, 66, 100, 136, 160, 256, 520])),
+                      vocab_size=int(rng.choice([23, 257, 512, 1000, 3001])), max_position_embeddings=1024,
+                      rms_norm_eps=float(rng.choice([1e-6, 1e-5, 3e-6])), rope_theta=float(rng.choice([1e4, 5e4, 1e6])),
+                      tie_word_embeddings=bool(rng.integers(0, 2)))
+    mdir = str(tmp_path / "model")
+    write_random_model(cfg, seed=trial, out_dir=mdir, weight_dtype="bfloat16",
+                       scales=InitScales(matrix=0.1, embedding=1.0, head=0.1, norm=0.1))
+    pc, pw = P.read_model(mdir)
+    plans = [(int(rng.choice([1, 2, 7, 33, 64, 65, 100, 130, 200, 300])), int(rng.integers(0, 12)))
+             for _ in range(int(rng.integers(1, 7)))]
+    toks = [rng.integers(0, cfg.vocab_size, size=p + n).tolist() for p, n in plans]
+    refs = [P.forward_logits(t, pc, pw) for t in toks]
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(Model.from_dir(mdir, dtype=dtype), max_tokens=4096)
+        for _ in range(2):
+            slots = [eng.new_sequence() for _ in plans]
+            got = eng.step([(s, t[:p]) for s, t, (p, n) in zip(slots, toks, plans)],
+                           [list(range(p)) for p, n in plans]).cpu().numpy()
+            at = 0
+            for i, (p, n) in enumerate(plans):
+                assert rel_err(got[at:at + p], refs[i][:p]) < TOL[dtype], (cfg, plans, dtype, "prompt", i)
+                at += p
+            for i, (p, n) in enumerate(plans):
+                if n == 0:
+                    eng.end_sequence(slots[i])
+            live, step = [i for i, (p, n) in enumerate(plans) if n > 0], 0
+            while live:
+                got = eng.step([(slots[i], [toks[i][plans[i][0] + step]]) for i in live]).cpu().numpy()
+                for j, i in enumerate(live):
+                    ref = refs[i][plans[i][0] + step]
+                    assert float(np.max(np.abs(got[j] - ref)) / np.max(np.abs(refs[i]))) < TOL[dtype], (cfg, plans, dtype, i, step)
+                step += 1
+                for i in [i for i in live if step >= plans[i][1]]:
+                    eng.end_sequence(slots[i])
+                live = [i for i in live if step < plans[i][1]]
+            eng.cache.check()
+            assert eng.cache.pages.held() == 0
