@@ -271,7 +271,7 @@ def gemm_algo(M: int, N: int, K: int) -> str:
     if M <= TC5_DECODE_MAX_ROWS // 2:
         # up to 128 rows the step is still bound by reading the weights: the decode kernel gives
         # every SM a share of them, the tiled kernel only where the output is wide enough for that
-        return "tc5_decode" if (N + 127) // 128 < 148 else "tc5"
+        return "tc5_decode" if (N + 127) // 128 < _sms() else "tc5"
     if M <= TC5_DECODE_MAX_ROWS and (N + 255) // 256 <= 16 and K >= 8192:
         return "tc5_decode"        # a narrow output with a long K: too few tiles for the tiled kernels
     if M >= TC5_PAIR_MIN_ROWS:
@@ -293,13 +293,18 @@ WIDE_OUTPUT = 32768
 _sm_count = {}
 
 
+def _sms() -> int:
+    """SMs of the current device."""
+    dev = torch.cuda.current_device()
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_count[dev]
+
+
 def _tc5_decode(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> None:
     M, K = a.shape
     N = w.shape[0]
-    dev = a.device
-    if dev not in _sm_count:
-        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
-    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sm_count[dev])))
+    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sms())))
     _check(_lib.gb_gemm_tc5_decode(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                    c_int64(a.stride(0)), c_int64(out.stride(0)), c_int(epi), c_int(splits), _stream()))
 
