@@ -360,6 +360,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    ap.add_argument("--points", default="1,64", help="batch sizes of the further decode points (default 1,64)")
     ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes (default: the benchmark's own, 8b)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length each sequence is filled to")
     ap.add_argument("--mixed", action="store_true",
@@ -403,7 +404,8 @@ def main():
                      "data": "synthetic: seeded random weights and token ids", "timing": "wall clock around the entry point's call"})
         print(json.dumps(line))
         return 0
-    max_batch = args.batch if args.no_points else max(args.batch, 64)
+    point_batches = [] if args.no_points else [int(b) for b in args.points.split(",") if b]
+    max_batch = max([args.batch] + point_batches)
     engine = Engine(model, max_tokens=max_batch * context, max_slots=max_batch, max_seq_tokens=context)
     fill_cache_random(engine, torch)
     sampler = DeviceSampler(cfg.vocab_size, max_batch, engine.device)
@@ -414,8 +416,17 @@ def main():
     clocks.start()
     dev = time_decode(engine, sampler, args.batch, args.steps, warmup, torch, ops)
     clock_info = clocks.stop()
-    # the generator prefills its own long prompts first, which leaves the GPU at the clocks of a
-    # compute-bound phase for some milliseconds: more untimed steps than the device-timed loop needs
+    prefill_ms, point_runs = None, {}
+    if not args.no_points:
+        prefill_ms = time_prefill(engine, PREFILL_TOKENS, iters=3, warmup=3, torch=torch)
+        for b in point_batches:
+            # after the prompt steps the GPU runs some milliseconds at the clocks of a compute-bound
+            # phase: more untimed steps than the headline run needs
+            point_runs[b] = time_decode(engine, sampler, b, args.steps, 16, torch, ops)
+    # the entry point makes an engine and a cache of its own: give this one's memory back first
+    del engine, sampler
+    torch.cuda.empty_cache()
+    # the generator prefills its own long prompts first (see above): 16 untimed steps here too
     e2e = time_entry_point(model, args.batch, args.steps, max(warmup, 16), context, torch)
 
     step_bytes = weight_bytes + kv_bytes_per_token * dev["kv_tokens"]
@@ -440,17 +451,14 @@ def main():
                      "frac": round(achieved / hbm_peak, 4)},
     }
     if not args.no_points:
-        ms = time_prefill(engine, PREFILL_TOKENS, iters=3, warmup=3, torch=torch)
+        ms = prefill_ms
         T = PREFILL_TOKENS
         params = (weight_bytes - model.head.numel() * model.head.element_size()) // 2
         flops = 2.0 * T * params + 2.0 * cfg.num_attention_heads * cfg.head_dim * T * T * layers + 2.0 * model.head.numel()
         line["prefill"] = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
                            "frac": round(flops / (ms * 1e-3) / (tflops_peak * 1e12), 4)}
         points = {}
-        for b in (1, 64):
-            # after the prompt steps the GPU runs some milliseconds at the clocks of a compute-bound
-            # phase: more untimed steps than the headline run needs
-            d = time_decode(engine, sampler, b, args.steps, 16, torch, ops)
+        for b, d in point_runs.items():
             points[f"decode_b{b}"] = round(b / (d["ms"] * 1e-3), 1)
             bytes_b = weight_bytes + kv_bytes_per_token * d["kv_tokens"]
             points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (d["ms"] * 1e-3) / 1e9 / hbm_peak, 4)
