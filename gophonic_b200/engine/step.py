@@ -268,9 +268,12 @@ class Engine:
             if have + len(toks) > self.capacity:
                 raise StepError(f"entry {i} (slot {slot}): {have} + {len(toks)} tokens exceed the per-sequence "
                                 f"capacity {self.capacity}")
-            for t in toks:
-                if not 0 <= int(t) < self.vocab:
-                    raise StepError(f"entry {i} (slot {slot}): token id {t} is outside [0, {self.vocab})")
+            ids = np.asarray(toks)
+            if ids.ndim != 1 or ids.dtype.kind not in "iu":
+                raise StepError(f"entry {i} (slot {slot}): tokens must be a flat sequence of integers")
+            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab:
+                t = int(ids[(ids < 0) | (ids >= self.vocab)][0])
+                raise StepError(f"entry {i} (slot {slot}): token id {t} is outside [0, {self.vocab})")
             if want is not None:
                 for w in want[i]:
                     if not 0 <= int(w) < len(toks):
