@@ -179,24 +179,32 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_decode_kernel(const __grid_c
     {
         uint32_t rank;
         asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
-        const int R = BMW / splits;  // rows of the tile this CTA adds up (16, 32 or 64)
+        const int R = BMW / splits;  // rows of the tile this CTA adds up (16, 32 or 64), four to a thread
+        const int R4 = R >> 2;
         const uint32_t part_addr = s32(tiles);
-        const int groups = (M * R + 31) / 32;
+        const int groups = (M * R4 + 31) / 32;
         for (int it = warp; it < groups; it += THREADS / 32) {
             const int idx = it * 32 + lane;
-            const int b = idx / R, nl = (int)rank * R + idx % R;
-            float v = 0.f;
+            const int b = idx / R4, nl = (int)rank * R + (idx % R4) * 4;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
             if (b < M) {
                 for (int sl = 0; sl < splits; sl++) {
                     uint32_t remote;
                     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(part_addr + (uint32_t)((b * BMW + nl) * 4)), "r"(sl));
-                    float x;
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(x) : "r"(remote) : "memory");
-                    v += x;
+                    float x0, x1, x2, x3;
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(x0), "=f"(x1), "=f"(x2), "=f"(x3) : "r"(remote) : "memory");
+                    v[0] += x0;
+                    v[1] += x1;
+                    v[2] += x2;
+                    v[3] += x3;
                 }
             }
-            float other = __shfl_down_sync(0xffffffffu, v, 8);
-            if (b < M) store_out<TC>(Y, ldy, b, n0 + nl, N, v, other, epi);
+            // the up rows of these four gate rows are eight rows on: two threads on, in the same batch row
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float other = __shfl_down_sync(0xffffffffu, v[e], 2);
+                if (b < M) store_out<TC>(Y, ldy, b, n0 + nl + e, N, v[e], other, epi);
+            }
         }
     }
     // no CTA may leave while another still reads its shared memory

@@ -163,17 +163,16 @@ def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def gemm_swiglu_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether ``gemm_swiglu`` takes this product: bfloat16, interleaved gate/up rows, and a row
-    count one of the kernels with the fused epilogue handles (up to 64, or at least 128)."""
-    return ((a.shape[0] <= 64 or a.shape[0] >= 128)
-            and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    """Whether ``gemm_swiglu`` takes this product: bfloat16 operands the tensor-core kernels accept,
+    gate/up rows interleaved in blocks of eight (every one of those kernels has the fused epilogue)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and w.shape[0] % 16 == 0 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
 
 
 def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto") -> None:
-    """out[M, N/2] = silu(a Wg^T) * (a Wu^T) in one kernel, for at most 64 rows; ``w`` [N, K] holds
-    gate and up rows interleaved in blocks of eight."""
+    """out[M, N/2] = silu(a Wg^T) * (a Wu^T) in one kernel, the one ``gemm`` would pick for a
+    product of these sizes; ``w`` [N, K] holds gate and up rows interleaved in blocks of eight."""
     _need(a, "gemm a", torch.bfloat16, 2, contiguous=False)
     _need(w, "gemm w", torch.bfloat16, 2)
     _need(out, "gemm out", dim=2, contiguous=False)
@@ -181,19 +180,21 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2) or out.stride(1) != 1 or not gemm_swiglu_accepts(a, w):
         raise KernelError(f"gemm_swiglu: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    if M >= TC5_PAIR_MIN_ROWS and algo != "tc5" or algo == "tc5_pair":
+    if algo == "auto":
+        algo = gemm_algo(M, N, K)
+    if algo == "tc5_pair":
         _check(_lib.gb_gemm_tc5_pair_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                             c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
-        return
-    if M > 64:
+    elif algo == "tc5":
         _check(_lib.gb_gemm_tc5_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                        c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
-        return
-    if M > SKINNY_MAX_ROWS and algo != "skinny" or algo == "tc5_decode":
+    elif algo == "tc5_decode":
         _tc5_decode(a, w, out, 1)
-        return
-    _check(_lib.gb_gemm_skinny_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
-                                      c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    elif algo == "skinny":
+        _check(_lib.gb_gemm_skinny_swiglu(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                          c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
+    else:
+        raise KernelError(f"gemm_swiglu: unknown algorithm '{algo}'")
 
 
 # ---- matrix products ---------------------------------------------------------------------

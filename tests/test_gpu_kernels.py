@@ -89,8 +89,8 @@ def test_swiglu(ops, dtype, inter):
     assert torch.isfinite(o).all() and o[0, 1] == 100.0 and abs(o[0, 0].item()) < 1e-30
 
 
-@pytest.mark.parametrize("M", [1, 8, 9, 33, 64, 128, 300])
-@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (1000, 96), (12288 // 8, 512)])
+@pytest.mark.parametrize("M", [1, 8, 9, 33, 64, 100, 128, 300])
+@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (1000, 96), (12288 // 8, 512), (4096, 2048)])  # the last: K slices
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
     """gate/up rows interleaved in blocks of eight; the few-row kernel applies silu(gate) * up itself,
@@ -101,7 +101,8 @@ def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
     g, u = x.double() @ gate.double().T, x.double() @ up.double().T
     ref = g / (1 + torch.exp(-g)) * u
     assert ops.gemm_swiglu_accepts(x, w)
-    for algo in (("skinny", "tc5_decode") if M <= 64 else ("tc5", "tc5_pair")):
+    algos = ["auto"] + (["skinny"] if M <= 64 else ["tc5", "tc5_pair"]) + (["tc5_decode"] if M <= ops.TC5_DECODE_MAX_ROWS else [])
+    for algo in algos:
         out = torch.full((M, inter), float("nan"), dtype=out_dtype, device=DEV)
         ops.gemm_swiglu(x, w, out, algo=algo)
         close(out, ref, 2e-5 if out_dtype == torch.float32 else 6e-3)
