@@ -28,7 +28,7 @@ class TensorDecl:
     """A tensor a part reads from the checkpoint.
 
     role: "matrix" (projection, [out, in]), "embedding" ([vocab, hidden]), "norm" (a scale
-    vector; initialised around 1), "vector" (initialised around 0), "table" (integers).
+    vector; initialised near 1), "vector" (initialised near 0), "table" (integers).
     ``optional``: absence is not an error (the tied head).
     """
     name: str
