@@ -37,6 +37,7 @@ def make_runtime(mode: str, device) -> Runtime:
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device is available; the engine has no CPU path")
     from .. import ops  # builds / loads the kernel library, or raises
+    ops.use_device(device.index if device.index is not None else torch.cuda.current_device())
     return Runtime(device=device, act_dtype=_DTYPES[mode], ops=ops)
 
 

@@ -42,11 +42,23 @@ def _code(dtype: torch.dtype) -> int:
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+_device_index = []
+
+
+def use_device(index: int) -> None:
+    """Make CUDA device ``index`` the current one and the one whose stream the kernels are launched
+    on.  The library serves one GPU at a time; a model opened on another device moves it there."""
+    torch.cuda.set_device(index)
+    _device_index[:] = [index]
+
+
 def _stream() -> c_void_p:
-    """torch's current CUDA stream of the current device, as a raw handle (asked anew at every call:
-    a graph capture runs on a stream of its own)."""
+    """torch's current CUDA stream of the library's device, as a raw handle (asked anew at every
+    call: a graph capture runs on a stream of its own)."""
     if _raw_stream is not None:
-        return c_void_p(_raw_stream(torch.cuda.current_device()))
+        if not _device_index:
+            _device_index.append(torch.cuda.current_device())
+        return c_void_p(_raw_stream(_device_index[0]))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -295,8 +307,8 @@ _sm_count = {}
 
 
 def _sms() -> int:
-    """SMs of the current device."""
-    dev = torch.cuda.current_device()
+    """SMs of the library's device."""
+    dev = _device_index[0] if _device_index else torch.cuda.current_device()
     if dev not in _sm_count:
         _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
     return _sm_count[dev]
