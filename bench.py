@@ -253,12 +253,14 @@ def probe(name):
         fn = (lambda: ops.gemm_swiglu(a, w, out)) if name.endswith("swiglu") else (lambda: ops.gemm(a, w, out))
         work = 2.0 * M * N * K
         unit = "TFLOP/s"
-    elif name in ("gemm_decode_b8", "gemm_decode_b64", "gemm_down_b128"):
+    elif name in ("gemm_decode_b8", "gemm_decode_b64", "gemm_down_b128", "gemm_o_b8"):
         M = 8 if name.endswith("b8") else 64
         N, K = 24576, 4096
         if name == "gemm_down_b128":   # the down projection of a step of 128 rows: K slices in clusters
             M, N, K = 128, 4096, 12288
-        ws = [rnd(N, K, scale=0.05) for _ in range(3 if N > 4096 else 6)]   # rotate 600 MB of weights through L2
+        if name == "gemm_o_b8":        # the narrowest product of a decode step
+            N, K = 4096, 4096
+        ws = [rnd(N, K, scale=0.05) for _ in range(max(3, int(6e8 / (2.0 * N * K))))]   # rotate 600 MB of weights through L2
         a = rnd(M, K)
         out = torch.empty((M, N), dtype=bf, device=dev)
         state = {"i": 0}
