@@ -81,13 +81,25 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_decode_kernel(const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
-    pdl_wait();  // barriers and tensor memory were set up while the kernel ahead was still running
+    // Barriers and tensor memory were set up while the kernel ahead was still running.  The weights
+    // do not depend on that kernel either: the loading thread requests the first stages' weights
+    // before it waits, and only their activations after.
+    const int early = KT < STAGES ? KT : STAGES;
+    if (warp == 0 && lane == 0) {
+        for (int kt = 0; kt < early; kt++) {
+            mbar_expect_tx(&full_bar[kt], STAGE_BYTES);
+            tma_load_2d(tiles + (size_t)kt * STAGE_BYTES, &map_w, (kb0 + kt) * BK, n0, &full_bar[kt]);
+        }
+    }
+    pdl_wait();
     pdl_trigger();
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kt = 0; kt < KT; kt++) {
+            int issued = early;
+            for (int kt = 0; kt < early; kt++)
+                tma_load_2d(tiles + (size_t)kt * STAGE_BYTES + W_BYTES, &map_x, (kb0 + kt) * BK, 0, &full_bar[kt]);
+            for (int kt = early; kt < KT; kt++) {
                 const int s = kt % STAGES;
                 const uint32_t phase = (uint32_t)(kt / STAGES) & 1u;
                 if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
