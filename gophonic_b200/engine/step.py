@@ -46,6 +46,7 @@ class StepBatch:
     sm_count: int = 148
     fixed_splits: Optional[int] = None
     _scratch: Dict[Tuple[int, int, int], torch.Tensor] = field(default_factory=dict)
+    _chosen: Dict[Tuple[int, int], int] = field(default_factory=dict)   # (kv heads, page bytes) -> splits, per batch
 
     def decode_splits(self, heads: int, kv_heads: int, head_dim: int, elem_bytes: int = 2) -> Tuple[int, Optional[torch.Tensor]]:
         """How many pieces single-token attention cuts each sequence's keys into, and the scratch
@@ -54,7 +55,10 @@ class StepBatch:
         if self.fixed_splits is not None:
             splits = self.fixed_splits
         else:
-            splits = choose_splits(self.nseq * kv_heads, self.max_kv_len, self.sm_count, 2 * 64 * head_dim * elem_bytes)
+            page_bytes = 2 * 64 * head_dim * elem_bytes
+            splits = self._chosen.get((kv_heads, page_bytes))
+            if splits is None:   # every attention layer of a step asks; the answer is the batch's
+                splits = self._chosen[(kv_heads, page_bytes)] = choose_splits(self.nseq * kv_heads, self.max_kv_len, self.sm_count, page_bytes)
         if splits <= 1:
             return 1, None
         key = (heads, head_dim, splits)
