@@ -15,9 +15,18 @@ way, by a layer's place among layers of its kind: internal/qwen3lm/gpu_darwin.go
 run's cache gets that run's plane, read-only.
 
 Slots.  ``alloc_slot`` hands out a free slot with length 0 and zeroed state; ``free_slot``
-returns its pages and the slot; both are reused.  Freed pages keep their old contents: nothing
-beyond a sequence's length is ever read.  Every mutation is checked first, so a refused call
-leaves the cache as it was (internal/qwen3lm/decode_batch.go:80-128 validates before mutating).
+returns its pages and the slot; both are reused.  A page is cleared, in every key/value plane,
+when it is handed to a sequence: the attention kernels mask what lies beyond a sequence's length
+but the tensor-core ones still multiply whole pages of values by probabilities of zero, and zero
+times an Inf or NaN that an earlier sequence left behind would not be zero.  So what a sequence
+can ever see in its pages is zeros or its own values (after a ``truncate``, its own old ones).
+Every mutation is checked first, so a refused call leaves the cache as it was
+(internal/qwen3lm/decode_batch.go:80-128 validates before mutating).
+
+A step's new pages reach the device as one list of (slot, logical page, physical page) triples:
+with kernels and an upload ring attached (``attach``, the engine does so) one pinned asynchronous
+copy and two small kernels write the block table and clear the pages, in stream order and without
+making the host wait; without them (tests on the CPU) torch indexing does the same.
 """
 from __future__ import annotations
 
@@ -161,6 +170,13 @@ class Cache:
         for key, planes in self._state_groups.items():
             shape, sdtype = key
             self._state[key] = torch.zeros((len(planes), self.max_slots) + tuple(shape), dtype=sdtype, device=self.device)
+        self._ops = None
+        self._stager = None
+
+    def attach(self, ops, stager) -> None:
+        """Use the kernel library (``block_table_set``, ``zero_pages``) and a pinned upload ring
+        (``upload(n, fill) -> device int32 tensor``) for the pages a step hands out."""
+        self._ops, self._stager = ops, stager
 
     # ---- description -------------------------------------------------------------------
     def groups(self) -> List[dict]:
@@ -242,16 +258,34 @@ class Cache:
         if need_total > self.pages.available():
             raise CacheFull(f"the step needs {need_total} more pages of {PAGE} tokens and {self.pages.available()} "
                             f"of {self.n_pages} are free")
+        triples: List[int] = []
         for slot, new_len in grow:
             have = len(self._pages_of[slot])
             want = pages_for(new_len)
-            if want <= have:
-                continue
-            fresh = [self.pages.take() for _ in range(have, want)]
-            self._pages_of[slot].extend(fresh)
-            # a small pageable source is staged by the driver before the call returns, so the list
-            # may change afterwards without touching the copy
-            self.block_table[slot, have:want].copy_(torch.tensor(fresh, dtype=torch.int32))
+            for lp in range(have, want):
+                page = self.pages.take()
+                self._pages_of[slot].append(page)
+                triples += (slot, lp, page)
+        if triples:
+            self._hand_out(triples)
+
+    def _hand_out(self, triples: List[int]) -> None:
+        """Write the block table entries of the (slot, logical, physical) triples and clear their pages."""
+        n = len(triples) // 3
+        if self._ops is not None and self._stager is not None:
+            def fill(buf):
+                buf[:] = triples
+            dev = self._stager.upload(3 * n, fill)
+            self._ops.block_table_set(self.block_table, dev, n)
+            for key in self._k:
+                self._ops.zero_pages(self._k[key], dev, n)
+                self._ops.zero_pages(self._v[key], dev, n)
+            return
+        t = torch.tensor(triples, dtype=torch.int64).view(n, 3).to(self.device)
+        self.block_table[t[:, 0], t[:, 1]] = t[:, 2].to(torch.int32)
+        for key in self._k:
+            self._k[key][:, t[:, 2]] = 0
+            self._v[key][:, t[:, 2]] = 0
 
     def commit(self, grow: Sequence[Tuple[int, int]]) -> None:
         for slot, new_len in grow:

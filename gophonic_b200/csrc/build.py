@@ -30,6 +30,7 @@ LIB_NAME = "libgophonic_b200.so"
 
 SOURCES = [
     "elementwise.cu",
+    "cache_fill.cu",
     "gemm_simt.cu",
     "gemm_mma.cu",
     "gemm_skinny.cu",

@@ -77,12 +77,13 @@ class Model:
     @classmethod
     def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0",
                     scales: InitScales = InitScales()) -> "Model":
-        """Random weights made on the device (for sizes too large to pass through a file)."""
+        """Random weights made on the device (for sizes too large to pass through a file): the tensors
+        ``write_random_model`` writes for the same configuration and seed, bit for bit."""
         mode = dtype_mode(dtype)
         spec = config.model_spec()
         rt = make_runtime(mode, device)
         tied = bool(getattr(config, "tie_word_embeddings", False))
-        tensors = random_tensors_on_device(spec, seed, mode, rt.device, scales, tied=tied)
+        tensors = random_tensors_on_device(spec, seed, mode, rt.device, scales, tied=tied, ops=rt.ops)
         return cls(spec, tensors, rt, config)
 
     # ---- description ---------------------------------------------------------------------

@@ -219,6 +219,7 @@ class Engine:
         self.vocab = model.spec.vocab
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.stager = HostStager(self.device)
+        self.cache.attach(model.rt.ops, self.stager)
         self._fetch_bufs: List[Optional[torch.Tensor]] = [None] * 4
         self._fetch_at = 0
         self.passes = 0

@@ -100,6 +100,37 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> N
                                 c_int(table.shape[0]), _ptr(out), _stream()))
 
 
+# ---- cache pages, seeded fill ------------------------------------------------------------
+def block_table_set(table: torch.Tensor, triples: torch.Tensor, n: int) -> None:
+    """table[slot, logical page] = physical page for the first ``n`` (slot, logical, physical)
+    triples of the int32 tensor ``triples``."""
+    _need(table, "block table", torch.int32, 2)
+    _need(triples, "page triples", torch.int32, 1)
+    if triples.numel() < 3 * n:
+        raise KernelError(f"block_table_set: {triples.numel()} integers for {n} triples")
+    _check(_lib.gb_block_table_set(_ptr(table), c_int(table.stride(0)), c_int(table.shape[0]), _ptr(triples), c_int(n), _stream()))
+
+
+def zero_pages(planes: torch.Tensor, triples: torch.Tensor, n: int) -> None:
+    """Clear, in every plane of ``planes`` [planes, pages, ...], the pages named by the third entry
+    of the first ``n`` triples."""
+    _need(planes, "cache planes", dim=None)
+    _need(triples, "page triples", torch.int32, 1)
+    if planes.dim() < 3 or triples.numel() < 3 * n:
+        raise KernelError(f"zero_pages: planes {tuple(planes.shape)}, {triples.numel()} integers for {n} triples")
+    es = planes.element_size()
+    _check(_lib.gb_zero_pages(_ptr(planes), c_int64(planes.stride(0) * es), c_int(planes.shape[0]), c_int64(planes.stride(1) * es),
+                              c_int(planes.shape[1]), _ptr(triples), c_int(n), _stream()))
+
+
+def random_fill(out: torch.Tensor, key: int, c: float, mean: float) -> None:
+    """The seeded fill of ``weights.random_init``: out[i] = (sum of eight 16-bit fields of two
+    splitmix64 words of (key, i) - 262140) * c + mean, the same bits the numpy writer computes."""
+    _need(out, "fill target")
+    _check(_lib.gb_random_fill(_ptr(out), _code(out.dtype), c_int64(out.numel()), c_uint64(key & 0xFFFFFFFFFFFFFFFF), c_float(c),
+                               c_float(mean), _stream()))
+
+
 # ---- norm --------------------------------------------------------------------------------
 def gather_tokens(ids: torch.Tensor, source: torch.Tensor) -> None:
     """ids[i] = source[ids[i]] in place (both int32 on the device)."""

@@ -54,6 +54,11 @@ def tiny_configs():
         "E": Qwen3Config(hidden_size=84, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3,
                          head_dim=16, intermediate_size=100, vocab_size=257, max_position_embeddings=600,
                          rms_norm_eps=1e-5, rope_theta=20000.0, tie_word_embeddings=True),
+        # the reference's own small test geometry (internal/qwen3lm/lmtest/lmtest.go:27-30): a head
+        # size that is no multiple of 16, attention wider than the hidden state, a vocabulary of 23
+        "F": Qwen3Config(hidden_size=96, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+                         head_dim=24, intermediate_size=136, vocab_size=23, max_position_embeddings=320,
+                         rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False),
     }
 
 

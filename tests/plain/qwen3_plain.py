@@ -52,6 +52,73 @@ def read_model(model_dir: str):
     return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"))
 
 
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    """The tensors of a Qwen3 dense checkpoint by name (internal/qwen3lm/weights.go:325-351); the
+    head only when the embeddings are not tied."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    heads, kvh = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = cfg.get("head_dim") or H // heads
+    out = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,)}
+    if not cfg.get("tie_word_embeddings", False):
+        out["lm_head.weight"] = (V, H)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        out.update({p + "input_layernorm.weight": (H,), p + "post_attention_layernorm.weight": (H,),
+                    p + "self_attn.q_proj.weight": (heads * d, H), p + "self_attn.k_proj.weight": (kvh * d, H),
+                    p + "self_attn.v_proj.weight": (kvh * d, H), p + "self_attn.o_proj.weight": (H, heads * d),
+                    p + "self_attn.q_norm.weight": (d,), p + "self_attn.k_norm.weight": (d,),
+                    p + "mlp.gate_proj.weight": (I, H), p + "mlp.up_proj.weight": (I, H), p + "mlp.down_proj.weight": (H, I)})
+    return out
+
+
+def seeded_values(seed: int, name: str, n: int, std: float, mean: float, first: int = 0) -> np.ndarray:
+    """The library's seeded fill, restated (elements first .. first + n - 1 of the flattened
+    tensor): element i of tensor ``name`` is made of the two
+    splitmix64 words 2i and 2i + 1 of the key sha256("seed:name")[:8] (little endian), word(j) =
+    finaliser(key + (j + 1) * 0x9E3779B97F4A7C15); the sum of their eight 16-bit fields, less
+    262140, times fp32(std / sqrt(2 (2^32 - 1) / 3)), plus the mean, each step rounded to fp32;
+    then rounded to bfloat16 as a BF16 checkpoint stores it.  Returned as float32 (exact)."""
+    import hashlib
+    key = np.uint64(int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little"))
+    c = np.float32(std / math.sqrt(2.0 * (2.0 ** 32 - 1.0) / 3.0))
+    out = np.empty(n, dtype=np.float32)
+    step = 1 << 21
+    with np.errstate(over="ignore"):
+        for lo in range(0, n, step):
+            hi = min(n, lo + step)
+            j = np.arange(2 * (first + lo), 2 * (first + hi), dtype=np.uint64)
+            x = key + (j + np.uint64(1)) * np.uint64(0x9E3779B97F4A7C15)
+            x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+            x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+            x = x ^ (x >> np.uint64(31))
+            s = np.zeros(2 * (hi - lo), dtype=np.int64)
+            for shift in (0, 16, 32, 48):
+                s += ((x >> np.uint64(shift)) & np.uint64(0xFFFF)).astype(np.int64)
+            s = s[0::2] + s[1::2] - 262140
+            out[lo:hi] = (s.astype(np.float32) * c).astype(np.float32) + np.float32(mean)
+    return bf16_round(out).astype(np.float32)
+
+
+def random_weights(cfg: dict, seed: int, matrix: float = 0.02, embedding: float = 0.02, head: float = 0.02,
+                   norm: float = 0.02, only=None) -> Dict[str, np.ndarray]:
+    """The tensors the library's random-weights mode makes for (cfg, seed): norm vectors centred on 1,
+    everything else on 0.  ``only``: a predicate on names, for models of which a test needs a part."""
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        if only is not None and not only(name):
+            continue
+        if name.endswith("norm.weight"):
+            std, mean = norm, 1.0
+        elif name == "model.embed_tokens.weight":
+            std, mean = embedding, 0.0
+        elif name == "lm_head.weight":
+            std, mean = head, 0.0
+        else:
+            std, mean = matrix, 0.0
+        out[name] = seeded_values(seed, name, int(np.prod(shape)), std, mean).reshape(shape)
+    return out
+
+
 def bf16_round(x: np.ndarray) -> np.ndarray:
     """Round to nearest even bfloat16 (internal/qwen3lm/lmtest/lmtest.go:136-140)."""
     b = np.asarray(x, dtype=np.float32).view(np.uint32)

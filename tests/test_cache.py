@@ -172,3 +172,27 @@ def test_key_splits_of_single_token_attention():
     assert choose_splits(640, 4096) in (3, 4)    # 80: two full waves and 48 CTAs
     assert choose_splits(896, 4096) == 1         # 112: three waves and more are left uncut
     assert choose_splits(5000, 4096) == 1
+
+
+def test_a_page_is_cleared_when_it_is_handed_out():
+    """What an earlier sequence left in a page (here: NaN everywhere) is gone when the page is given
+    to another one, in every plane of every group; pages nobody was given keep their contents."""
+    c = make(max_tokens=64 * 6, requests=[(KVRequest(2, 16), None), (KVRequest(1, 8, 32), None), (KVRequest(2, 16), None)])
+    for group in (c._k, c._v):
+        for t in group.values():
+            t.fill_(float("nan"))
+    s = c.alloc_slot()
+    c.reserve([(s, 130)])
+    held = c._pages_of[s]
+    assert len(held) == 3 and c.block_table[s, :3].tolist() == held
+    free = [p for p in range(c.n_pages) if p not in held]
+    for group in (c._k, c._v):
+        for t in group.values():
+            assert (t[:, held] == 0).all()
+            assert torch.isnan(t[:, free]).all()
+    c.commit([(s, 130)])
+    c.reserve([(s, 193)])       # one more page: only that one is cleared, the sequence's own stay
+    c._k[(2, 16, 0)][:, held[0]] = 5.0
+    c.reserve([(s, 200)])
+    assert (c._k[(2, 16, 0)][:, held[0]] == 5.0).all()
+    c.check()

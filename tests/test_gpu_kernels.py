@@ -175,6 +175,66 @@ def test_gemm_adds_into_the_residual(ops, M, N, K):
     assert not ops.gemm_add_accepts(small, w, torch.empty((8, N), device=DEV))
 
 
+# Sizes of a full-size layer: every CTA of the persistent kernels computes several tiles one after
+# the other (768 tiles of 256 x 256 on 74 pairs, 1536 of 128 x 256 on 148 CTAs), so both tensor-memory
+# accumulators are handed back more than once, the stage ring runs on across tiles and the staging
+# buffers of the reducing epilogue are used again; one ragged size whose last tiles hang over.
+FULL_SIZE = [(2048, 24576, 4096), (2048, 4096, 12288), (2048, 6144, 4096), (150, 24576, 4096), (1000, 5000, 4104)]
+
+
+def _close_wide(got: torch.Tensor, ref: torch.Tensor, tol: float):
+    """As ``close``, on the device (the products are hundreds of megabytes), and naming the first
+    bad element: its tile says which round of the tile loop went wrong."""
+    err = (got.double() - ref).abs()
+    scale = ref.abs().max().item()
+    worst = err.max().item() / scale
+    if not worst < tol:
+        at = int(torch.nonzero(err.flatten() >= tol * scale)[0])
+        r, c = divmod(at, ref.shape[1])
+        raise AssertionError(f"relative error {worst:.3e} >= {tol}; first bad element ({r}, {c}), "
+                             f"tile of 256 x 256 ({r // 256}, {c // 256})")
+    assert torch.isfinite(got).all()
+
+
+@pytest.mark.parametrize("M,N,K", FULL_SIZE)
+def test_gemm_tiled_kernels_walk_many_tiles_per_cta(ops, M, N, K):
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+    ref = a.double() @ w.double().T
+    for algo in ("tc5", "tc5_pair"):
+        for out_dtype in (torch.float32, torch.bfloat16):
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            ops.gemm(a, w, out, algo=algo)
+            assert ops.tc5_status() == 0, "a tcgen05 kernel gave up waiting on a barrier"
+            _close_wide(out, ref, 2e-5 if out_dtype == torch.float32 else 6e-3)
+    # the epilogue that adds into the fp32 residual: the bits of product-then-add, and the float64 sum
+    h0 = rnd(M, N, seed=3)
+    prod = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ops.gemm(a, w, prod, algo="tc5_pair")
+    h = h0.clone()
+    ops.gemm_add(a, w, h)
+    assert ops.tc5_status() == 0
+    assert torch.equal(h, h0 + prod)
+    _close_wide(h, h0.double() + ref, 2e-5)
+    # twice in a row into the same residual, as two layers do
+    ops.gemm_add(a, w, h)
+    assert torch.equal(h, (h0 + prod) + prod)
+
+
+@pytest.mark.parametrize("M,inter,K", [(2048, 12288, 4096), (150, 12288, 4096), (1000, 2504, 4104)])
+def test_gemm_swiglu_tiled_kernels_walk_many_tiles_per_cta(ops, M, inter, K):
+    gate, up = rnd(inter, K, dtype=torch.bfloat16, scale=0.05, seed=1), rnd(inter, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    w = torch.stack([gate.view(inter // 8, 8, K), up.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
+    x = rnd(M, K, dtype=torch.bfloat16, seed=3)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    ref = g / (1 + torch.exp(-g)) * u
+    for algo in ("tc5", "tc5_pair", "auto"):
+        for out_dtype in (torch.float32, torch.bfloat16):
+            out = torch.full((M, inter), float("nan"), dtype=out_dtype, device=DEV)
+            ops.gemm_swiglu(x, w, out, algo=algo)
+            assert ops.tc5_status() == 0
+            _close_wide(out, ref, 2e-5 if out_dtype == torch.float32 else 6e-3)
+
+
 def test_gemm_dispatch_never_puts_float32_on_tensor_cores(ops):
     a, w = rnd(4, 64), rnd(8, 64)
     out = torch.empty((4, 8), device=DEV)
@@ -374,6 +434,20 @@ def test_attention_single_tokens(ops, dtype, algo, heads, kvh, d, splits):
         assert used == "decode_mma"
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kvh,d", [(8, 2, 24), (3, 1, 40), (2, 2, 6)])
+def test_attention_head_sizes_that_are_no_multiple_of_16(ops, dtype, heads, kvh, d):
+    """Even head sizes between the steps of 16 (the reference's own test shape has 24) run on the
+    CUDA-core kernel in both dtypes: prompts, continued prompts, single tokens with key splits."""
+    out, ref, used = attention_case(ops, dtype, heads, kvh, d, q_lens=[70, 5, 1, 33], kv_lens=[70, 69, 130, 33])
+    assert used == "simt"
+    close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+    for splits in (1, 3):
+        out, ref, used = attention_case(ops, dtype, heads, kvh, d, q_lens=[1, 1, 1], kv_lens=[1, 700, 65], splits=splits)
+        assert used == "simt"
+        close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+
+
 def test_attention_head_sizes_without_a_tensor_core_kernel_fall_back(ops):
     out, ref, used = attention_case(ops, torch.bfloat16, 2, 1, 144, q_lens=[40, 1], kv_lens=[40, 90])
     assert used == "simt"
@@ -384,10 +458,12 @@ def test_attention_head_sizes_without_a_tensor_core_kernel_fall_back(ops):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("algo", ["simt", "auto"])
-def test_attention_finds_one_far_key_among_hundreds(ops, dtype, algo):
+@pytest.mark.parametrize("heads,kvh,d", [(4, 2, 64), (8, 2, 128), (8, 2, 24)])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, algo, heads, kvh, d):
     """One query and one key 500 positions back are scaled so that key takes all the weight: the
-    output must be that key's value, for a prompt row and for a single-token row."""
-    heads, kvh, d = 4, 2, 64
+    output must be that key's value, for a prompt row and for a single-token row.  At head_dim 128
+    the prompt runs on the tcgen05 kernel and the single tokens on the mma.sync one; head_dim 24
+    has no tensor-core kernel."""
     far = 37
 
     def craft(q, k_plane, v_plane, table, slots):
@@ -420,6 +496,39 @@ def test_attention_window_edge(ops, dtype, algo):
             q[:, 5::d] = 40.0
         out, ref, _ = attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, window=w, craft=craft, algo=algo)
         close(out, ref, 1e-5 if dtype == torch.float32 else 1.2e-2)
+
+
+@pytest.mark.parametrize("algo", ["prefill_tc5", "prefill_mma", "simt"])
+def test_attention_rescales_its_running_output_by_a_real_factor(ops, algo):
+    """The tcgen05 kernel rescales O only when a row's maximum outgrew the scale in use by more than
+    2^8.  Random scores never do that after the first page, so the inputs are made to: key A (second
+    page) lifts the maximum by 2^7.3, just under the threshold (no rescale, probabilities up to 158
+    rounded to bfloat16); key B (fourth page) lifts it by 2^8.5 over the scale in use, so O and the row
+    sum are multiplied by 2^-8.5, after which the old keys, A and B each hold about a third of the
+    weight: a factor that is wrong, or applied to only one of O and the sum, moves the output by
+    tens of per cent.  Every other row has a weak query and keeps its scale, so a warp holds rows
+    that rescale beside rows that multiply by one.  A second prompt continues a cached prefix."""
+    heads, kvh, d = 4, 2, 128
+    pos_a, pos_b = 100, 200
+    unit = (1.0 / math.sqrt(d)) * 1.4426950408889634          # one raw score in the kernel's base-2 units
+
+    def craft(q, k_plane, v_plane, table, slots):
+        k_plane.mul_(0.25)
+        k_plane[..., 3] = 0      # ordinary keys score within a few hundredths of zero
+        for slot in slots:
+            for pos, lift in ((pos_a, 7.5), (pos_b, 8.7)):
+                page, off = table[slot, pos // 64].item(), pos % 64
+                k_plane[page, :, off] = 0
+                k_plane[page, :, off, 3] = lift / (8.0 * unit)
+        q.mul_(0.05)
+        q[0::2, 3::d] = 8.0      # strong rows: scores of A and B stand 7.5 and 8.7 above the rest
+        q[1::2, 3::d] = 0.5      # weak rows: nothing grows
+    out, ref, used = attention_case(ops, torch.bfloat16, heads, kvh, d, q_lens=[300, 70], kv_lens=[300, 400], algo=algo,
+                                    seed=5, craft=craft)
+    assert used == algo and ops.tc5_status() == 0
+    close(out, ref, 1.2e-2)
+    # the case is what it claims: on a strong row past B, neither B nor the keys before it are negligible
+    assert ref[298].abs().max() > 0
 
 
 def test_attention_refuses_what_it_cannot_take(ops):

@@ -101,6 +101,62 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(model_dirs, tmp_pat
         assert word in msg
 
 
+def test_tensors_nobody_declared_are_left_alone_unless_strict(model_dirs, tmp_path):
+    """A snapshot that carries a tensor beyond the model's own loads (the reference resolves by name
+    and ignores the rest: internal/qwen3lm/weights.go:291-351); the name is reported in a warning,
+    and ``strict`` turns it into the error."""
+    def edit(t):
+        t["model.rotary_emb.inv_freq"] = ("F32", (8,), np.zeros(8, dtype=np.float32))
+    d = str(tmp_path / "extra")
+    _rewrite(model_dirs["A"], d, edit)
+    decls = declare_model(tiny_configs()["A"].model_spec())
+    with pytest.warns(UserWarning, match="model.rotary_emb.inv_freq"):
+        t = load_tensors(d, decls, "bfloat16", "cpu")
+    assert "model.rotary_emb.inv_freq" not in t and "model.norm.weight" in t
+    with pytest.raises(WeightsError) as ei:
+        load_tensors(d, decls, "bfloat16", "cpu", strict=True)
+    assert ei.value.unexpected == ["model.rotary_emb.inv_freq"] and not ei.value.missing
+
+
+def test_half_precision_matrices_are_widened_not_rounded(model_dirs, tmp_path):
+    """An F16 matrix has three more mantissa bits than bfloat16: it becomes float32, exactly, in both
+    modes (the reference refuses matrices that are not BF16: internal/qwen3lm/weights.go:754-756)."""
+    vals = (np.arange(64 * 64, dtype=np.float32).reshape(64, 64) / 4096 + 1 / 1024).astype(np.float16)
+
+    def edit(t):
+        t["model.layers.0.self_attn.o_proj.weight"] = ("F16", (64, 64), vals.reshape(-1).copy())
+    d = str(tmp_path / "half")
+    _rewrite(model_dirs["A"], d, edit)
+    decls = declare_model(tiny_configs()["A"].model_spec())
+    for mode in ("bfloat16", "float32"):
+        t = load_tensors(d, decls, mode, "cpu")["model.layers.0.self_attn.o_proj.weight"]
+        assert t.dtype == torch.float32 and np.array_equal(t.numpy(), vals.astype(np.float32))
+
+
+def test_the_same_seed_gives_the_same_bits_on_every_path(tmp_path):
+    """One fill for the folder writer and for whoever restates it: element i of a tensor depends on
+    (seed, tensor name, i) alone.  The plain implementation's own restatement of the formula gives
+    the writer's bits; the values have the wanted mean and deviation."""
+    from gophonic_b200.weights import InitScales, write_random_model
+    from gophonic_b200.weights.random_init import counter_fill, fill_constant
+    from tests.plain import qwen3_plain as P
+    cfg = tiny_configs()["B"]
+    d = str(tmp_path / "m")
+    scales = InitScales(matrix=0.02, embedding=0.5, head=0.1, norm=0.05)
+    write_random_model(cfg, seed=11, out_dir=d, weight_dtype="bfloat16", scales=scales)
+    _, stored = P.read_model(d)
+    made = P.random_weights(json.load(open(os.path.join(d, "config.json"))), 11, matrix=0.02, embedding=0.5, head=0.1, norm=0.05)
+    assert sorted(stored) == sorted(made)
+    for name in stored:
+        assert np.array_equal(stored[name], made[name]), name
+    # a tensor cut anywhere is the same tensor; the moments are the normal law's
+    whole = counter_fill(12345, (1 << 22) + 77, 0.02, 0.0)
+    assert np.array_equal(whole[:1000], counter_fill(12345, 1000, 0.02, 0.0))
+    assert abs(float(whole.mean())) < 1e-4 and abs(float(whole.std()) / 0.02 - 1) < 2e-3
+    assert float(np.abs(whole).max()) <= 262140 * float(fill_constant(0.02)) * 1.0001
+    assert abs(float(counter_fill(9, 1 << 16, 0.05, 1.0).mean()) - 1.0) < 1e-3
+
+
 def test_untied_model_without_head_reports_it_only_if_it_cannot_tie(model_dirs, tmp_path):
     # Qwen3's head may always be tied to the embedding: a checkpoint without lm_head loads
     def edit(t):
