@@ -114,6 +114,14 @@ class StateView:
     writable: bool
 
 
+@dataclass
+class CacheMark:
+    """What ``Cache.snapshot`` returns: a length and the state of that moment."""
+    slot: int
+    length: int
+    state: Dict[object, torch.Tensor]
+
+
 class Cache:
     def __init__(self, requests: Sequence[Tuple[object, Optional[int]]], max_tokens: int, device,
                  dtype: torch.dtype, max_slots: Optional[int] = None, max_seq_tokens: Optional[int] = None):
@@ -293,7 +301,9 @@ class Cache:
 
     def truncate(self, slot: int, n: int) -> None:
         """Forget everything after the first ``n`` tokens of a sequence.  Only key/value planes can
-        be cut; a model with fixed-size state cannot rewind it."""
+        be cut at any position; a model with fixed-size state goes back to a ``snapshot`` instead.
+        The pages past the cut go back to the pool; the kept last page still holds the sequence's
+        old keys and values beyond ``n``, which are overwritten before anything can attend to them."""
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not live")
         if not 0 <= n <= self._length[slot]:
@@ -304,6 +314,31 @@ class Cache:
         while len(self._pages_of[slot]) > keep:
             self.pages.give(self._pages_of[slot].pop())
         self._length[slot] = n
+
+    def snapshot(self, slot: int) -> "CacheMark":
+        """A mark of the sequence as it is: its length and a copy of its fixed-size state.  Keys and
+        values are not copied (what lies below the mark's length stays where it is as the sequence
+        grows), so a mark is only good for going back, while the sequence lives."""
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is not live")
+        return CacheMark(slot, self._length[slot], {key: t[:, slot].clone() for key, t in self._state.items()})
+
+    def restore(self, slot: int, mark: "CacheMark") -> None:
+        """Go back to ``mark``: forget the keys and values after its length and put its state back.
+        This is how a sequence with fixed-size state is rewound (``truncate`` cannot: a state has no
+        positions to cut at)."""
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is not live")
+        if mark.slot != slot:
+            raise CacheError(f"the mark was taken of slot {mark.slot}, not of slot {slot}")
+        if mark.length > self._length[slot]:
+            raise CacheError(f"slot {slot}: the mark lies at {mark.length} tokens, beyond its {self._length[slot]}")
+        keep = pages_for(mark.length)
+        while len(self._pages_of[slot]) > keep:
+            self.pages.give(self._pages_of[slot].pop())
+        self._length[slot] = mark.length
+        for key, saved in mark.state.items():
+            self._state[key][:, slot].copy_(saved)
 
     def check(self) -> None:
         """Invariants: no slot or page lost, held twice, or held by a dead slot."""

@@ -35,9 +35,15 @@ class Request:
     budget: int                      # most tokens this reply may have
     seed: int
     reply: List[int] = field(default_factory=list)
-    slot: Optional[int] = None
+    slot: Optional[int] = None       # given by the caller (with ``keep_slot``) or taken by the loop
     row: Optional[int] = None        # lane of the running batch (the sampler's row)
     finished: Optional[str] = None   # "stop" | "length"
+    # A request that continues a sequence its caller owns (a chat session's slot): ``prompt`` holds
+    # only the tokens the cache does not hold yet, and the slot is not given back at the end.
+    keep_slot: bool = False
+    # every token the loop fed to the engine after the prompt, in order: with ``prompt`` what the
+    # slot holds more than before (a stop token that a step ran ahead of is among them)
+    fed: List[int] = field(default_factory=list)
 
 
 @dataclass
@@ -124,6 +130,14 @@ class Generator:
                 results[r.index] = r.reply
         return results
 
+    def run(self, batch: List[Request], on_token=None) -> None:
+        """Run requests the caller made itself as one batch that starts together: each request's
+        ``prompt`` in one step, then one token each, until every request has finished.  A request
+        with ``keep_slot`` continues the sequence in its ``slot`` and keeps it afterwards."""
+        if not batch or len(batch) > self.max_batch:
+            raise GenerationError(f"a batch of {len(batch)} requests (at most {self.max_batch})")
+        self._run_batch(batch, on_token)
+
     def _run_batch(self, batch: List[Request], on_token) -> None:
         if all(hasattr(self.engine, a) for a in ("step_from", "fetch_tokens")) and hasattr(self.sampler, "select_device"):
             return self._run_batch_ahead(batch, on_token)
@@ -131,9 +145,7 @@ class Generator:
         live: List[Request] = []
         try:
             for row, r in enumerate(batch):
-                r.slot = self.engine.new_sequence()
-                r.row = row
-                self.sampler.start(row, r.options, r.seed)
+                self._begin(r, row)
                 live.append(r)
             # all prompts in one step
             logits = self.engine.step([(r.slot, r.prompt) for r in live])
@@ -146,20 +158,19 @@ class Generator:
                     if r.finished is None:
                         still.append(r)
                     else:
-                        self.engine.end_sequence(r.slot)
-                        r.slot = None
+                        self._release(r)
                 live = still
                 if not live:
                     break
                 # one token each
                 logits = self.engine.step([(r.slot, [r.reply[-1]]) for r in live])
+                for r in live:
+                    r.fed.append(r.reply[-1])
                 self.stats.decode_steps += 1
                 self.stats.decoded_tokens += len(live)
         finally:
             for r in batch:
-                if r.slot is not None:
-                    self.engine.end_sequence(r.slot)
-                    r.slot = None
+                self._release(r)
 
     def _run_batch_ahead(self, batch: List[Request], on_token) -> None:
         """The same batch with the next step enqueued before the last one's tokens are read."""
@@ -167,9 +178,7 @@ class Generator:
         try:
             live: List[Request] = []
             for row, r in enumerate(batch):
-                r.slot = self.engine.new_sequence()
-                r.row = row
-                self.sampler.start(row, r.options, r.seed)
+                self._begin(r, row)
                 live.append(r)
             logits = self.engine.step([(r.slot, r.prompt) for r in live])
             self.stats.prefill_tokens += sum(len(r.prompt) for r in live)
@@ -187,15 +196,17 @@ class Generator:
                     nxt = ([r for _, r in ahead], nxt_drawn, self.engine.fetch_tokens(nxt_drawn))
                 # read and handle the tokens of the step before while the one just enqueued runs
                 going = 0
+                fed_ahead = {id(r) for _, r in ahead}
                 for r, t in zip(live, fetch.wait()):
                     if r.finished is not None:
                         continue  # it drew a stop token a step ago: this entry ran for nothing
+                    if id(r) in fed_ahead:
+                        r.fed.append(int(t))   # the step just enqueued stores it, whatever it turns out to be
                     self._take(r, int(t), on_token)
                     if r.finished is None:
                         going += 1
                     else:
-                        self.engine.end_sequence(r.slot)
-                        r.slot = None
+                        self._release(r)
                 if nxt is None:
                     break
                 live, drawn, fetch = nxt
@@ -206,9 +217,21 @@ class Generator:
                 self.stats.decoded_tokens += going
         finally:
             for r in batch:
-                if r.slot is not None:
-                    self.engine.end_sequence(r.slot)
-                    r.slot = None
+                self._release(r)
+
+    def _begin(self, r: Request, row: int) -> None:
+        if not r.keep_slot:
+            r.slot = self.engine.new_sequence()
+        elif r.slot is None:
+            raise GenerationError(f"request {r.index} keeps its slot and has none")
+        r.row = row
+        self.sampler.start(row, r.options, r.seed)
+
+    def _release(self, r: Request) -> None:
+        """Give the sequence's slot and pages back, unless its caller owns them."""
+        if r.slot is not None and not r.keep_slot:
+            self.engine.end_sequence(r.slot)
+            r.slot = None
 
     def _take(self, r: Request, token: int, on_token) -> None:
         if token in self.stop_ids:

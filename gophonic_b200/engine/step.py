@@ -243,6 +243,31 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def truncate(self, slot: int, n: int) -> None:
+        """Forget everything after the first ``n`` tokens of the sequence in ``slot``: the next step
+        goes on from position ``n`` (internal/qwen3lm/evaluator.go:185-226 keeps a prefix of its
+        key/value store the same way; a chat session that branches, or whose last reply was cut
+        short, lives on it).  Refused for a model whose mixers keep fixed-size state, which has no
+        positions to cut at: use ``checkpoint`` / ``restore``."""
+        try:
+            self.cache.truncate(slot, n)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+
+    def checkpoint(self, slot: int):
+        """A mark of the sequence as it is (its length and a copy of its fixed-size state) for ``restore``."""
+        try:
+            return self.cache.snapshot(slot)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+
+    def restore(self, slot: int, mark) -> None:
+        """Go back to a mark taken of this sequence earlier: works for every kind of mixer."""
+        try:
+            self.cache.restore(slot, mark)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+
     def check_kernels(self) -> None:
         """Raise if a kernel recorded that it gave up waiting on a barrier (synchronises)."""
         code = self.model.rt.ops.tc5_status()

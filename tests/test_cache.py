@@ -196,3 +196,32 @@ def test_a_page_is_cleared_when_it_is_handed_out():
     c.reserve([(s, 200)])
     assert (c._k[(2, 16, 0)][:, held[0]] == 5.0).all()
     c.check()
+
+
+def test_marks_bring_a_sequence_back_with_its_state():
+    c = make(max_tokens=64 * 6, requests=[(KVRequest(2, 16), None), (StateRequest((3,), torch.float32), None)])
+    s = c.alloc_slot()
+    c.reserve([(s, 70)])
+    c.commit([(s, 70)])
+    state = c.view(1).state
+    state[s] = torch.tensor([1.0, 2.0, 3.0])
+    mark = c.snapshot(s)
+    c.reserve([(s, 200)])
+    c.commit([(s, 200)])
+    state[s] = torch.tensor([9.0, 9.0, 9.0])
+    assert c.pages.held() == 4
+    with pytest.raises(CacheError, match="cannot be truncated"):
+        c.truncate(s, 70)
+    c.restore(s, mark)
+    assert c.length(s) == 70 and c.pages.held() == 2 and state[s].tolist() == [1.0, 2.0, 3.0]
+    c.check()
+    other = c.alloc_slot()
+    with pytest.raises(CacheError, match="not of slot"):
+        c.restore(other, mark)
+    c.truncate(s, 70)      # to its own length: nothing to cut
+    c.restore(s, mark)
+    c.reserve([(s, 64)]) if False else None
+    c.free_slot(s)
+    with pytest.raises(CacheError, match="not live"):
+        c.restore(s, mark)
+    c.check()

@@ -341,6 +341,49 @@ def test_what_an_earlier_request_left_in_a_page_is_never_seen(model_dirs, refere
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("cut", [90, 128, 1])
+def test_a_sequence_rewound_and_continued_equals_a_fresh_one(engines, references, plain_models, name, dtype, cut):
+    """A prompt of 150, then 32 tokens one by one; back to ``cut`` tokens (inside a page, on a page's
+    edge, to the very first token); 40 other tokens in one step, then single tokens; back once more
+    and on by one token.  Every step's logits are those of a fresh evaluation of the same ids: what
+    the kept last page still holds of the forgotten tokens is never seen
+    (internal/qwen3lm/weights_test.go:189-275 walks its prefix store through the same moves)."""
+    eng = engines(name, dtype)
+    cfg, _ = plain_models[name]
+    rng = np.random.default_rng(77 + cut)
+    first = rng.integers(0, cfg["vocab_size"], size=182).tolist()
+    other = rng.integers(0, cfg["vocab_size"], size=45).tolist()
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, first[:150])], [list(range(150))]).cpu().numpy()]
+    for t in first[150:]:
+        got.append(eng.step([(slot, [t])]).cpu().numpy())
+    bad = first_bad_row(np.concatenate(got, 0), references(name, first), dtype)
+    assert bad is None, f"before the rewind: first wrong position {bad[0]} ({bad[1]})"
+    held = eng.cache.pages.held()
+    eng.truncate(slot, cut)
+    assert eng.length(slot) == cut and eng.cache.pages.held() == (cut + 63) // 64 <= held
+    branch = first[:cut] + other
+    got = [eng.step([(slot, other[:40])], [list(range(40))]).cpu().numpy()]
+    for t in other[40:]:
+        got.append(eng.step([(slot, [t])]).cpu().numpy())
+    bad = first_bad_row(np.concatenate(got, 0), references(name, branch)[cut:], dtype)
+    assert bad is None, f"after the rewind to {cut}: first wrong position {cut + bad[0]} ({bad[1]})"
+    # back again, to the middle of the branch, and on by one token
+    eng.truncate(slot, cut + 7)
+    again = branch[:cut + 7] + [first[3]]
+    out = eng.step([(slot, [first[3]])]).cpu().numpy()
+    bad = first_bad_row(out, references(name, again)[-1:], dtype)
+    assert bad is None, f"after the second rewind: {bad[1]}"
+    from gophonic_b200.engine import StepError
+    with pytest.raises(StepError, match="cannot truncate"):
+        eng.truncate(slot, eng.length(slot) + 1)
+    eng.end_sequence(slot)
+    eng.cache.check()
+    assert eng.cache.pages.held() == 0
+
+
 def test_where_a_sequence_lies_in_the_cache_changes_nothing(engines, plain_models):
     eng = engines("A", "float32", 1024)
     cfg, _ = plain_models["A"]
