@@ -4,12 +4,12 @@ Importing the package needs no GPU.  The kernel library is compiled and loaded t
 model is opened on a CUDA device.
 """
 from . import registry
-from .api import (ChatOptions, Detect, ErrUnknownFormat, ErrUnsupported, Format, FormatBF16, FormatF32, Formats,
+from .api import (ChatGeneratorLane, ChatOptions, Detect, ErrUnknownFormat, ErrUnsupported, Format, FormatBF16, FormatF32, Formats,
                   Lane, Open, OpenedModel, Options, Provide, Register, Supports, TokensGenerator)
 from .config import ConfigError, Qwen3Config
 
 __version__ = "0.1.0"
 
-__all__ = ["ChatOptions", "ConfigError", "Detect", "ErrUnknownFormat", "ErrUnsupported", "Format", "FormatBF16",
+__all__ = ["ChatGeneratorLane", "ChatOptions", "ConfigError", "Detect", "ErrUnknownFormat", "ErrUnsupported", "Format", "FormatBF16",
            "FormatF32", "Formats", "Lane", "Open", "OpenedModel", "Options", "Provide", "Qwen3Config", "Register",
            "Supports", "TokensGenerator", "registry"]

@@ -10,8 +10,9 @@ registered later are tried first, so a registered format can take over paths a b
 matches (gophonic.go:176-186).  What a model can do is the set of lanes it provides; ``Lane``
 opens one and ``Supports`` reports whether it can (gophonic.go:89-124).  The built-in format
 matches a folder whose config.json names a registered architecture (qwen3/model.go:110-129 reads
-``model_type`` the same way) and provides the lane "tokens.Generator": generation over token
-ids.  Text lanes need a tokenizer, which this library does not have.
+``model_type`` the same way) and provides two lanes: "tokens.Generator", batched generation over
+token ids, and "chat.Generator", conversations whose context stays evaluated between replies
+(``gophonic_b200.chat``; text where the folder has a tokenizer.json, token ids otherwise).
 """
 from __future__ import annotations
 
@@ -28,6 +29,7 @@ FormatBF16 = "bf16"   # bfloat16 weights and activations on the tensor cores, fp
 FormatF32 = "f32"     # everything in true 32-bit, no reduced-precision matrix mode
 
 TokensGenerator = "tokens.Generator"
+ChatGeneratorLane = "chat.Generator"
 
 
 class ErrUnknownFormat(ValueError):
@@ -204,13 +206,84 @@ class TokenGenerator:
         self.engine = None
 
 
+def _open_chat(model, opts: Options, path: str):
+    """Lane "chat.Generator" over a model: sessions that keep their context evaluated."""
+    from .chat import ChatGenerator, Template
+    from .engine.step import Engine
+    from .sampling.sampler import DeviceSampler
+    from .tokenizer import load_tokenizer
+    cfg = model.config
+    context = int(getattr(cfg, "max_position_embeddings", model.spec.max_positions))
+    tokens = opts.CacheTokens or min(context, 4096) * opts.Batch
+    engine = Engine(model, max_tokens=tokens, max_seq_tokens=min(context, tokens))
+    sampler = DeviceSampler(model.spec.vocab, 1, model.rt.device)
+    tokenizer = load_tokenizer(path)
+    if tokenizer is not None and tokenizer.added_id("<|im_end|>") is not None:
+        template = Template.qwen3(tokenizer, thinking_block=tokenizer.template_thinks)
+    else:
+        template = Template(stop=read_stop_ids(path))
+    return ChatGenerator(engine, sampler, min(context, engine.capacity), template, tokenizer)
+
+
 def _open_dir(path: str, opts: Options) -> OpenedModel:
     from .engine.model import Model
     mode = "float32" if opts.Format == FormatF32 else "bfloat16"
     model = Model.from_dir(path, dtype=mode, device=opts.Device)
     m = OpenedModel(model.spec.architecture, path)
     m.model = model
-    return Provide(m, TokensGenerator, lambda: TokenGenerator(model, opts, read_stop_ids(path)))
+    Provide(m, TokensGenerator, lambda: TokenGenerator(model, opts, read_stop_ids(path)))
+    return Provide(m, ChatGeneratorLane, lambda: _open_chat(model, opts, path))
 
 
-Register(Format(Name="model-folder", Match=_is_model_dir, Open=_open_dir, Provides=(TokensGenerator,)))
+Register(Format(Name="model-folder", Match=_is_model_dir, Open=_open_dir, Provides=(TokensGenerator, ChatGeneratorLane)))
+
+
+# ---- random weights by name ---------------------------------------------------------------------
+RANDOM_PREFIX = "random:"
+
+
+def random_model_path(name: str, seed: int = 0, layers: int = 0) -> str:
+    """The path that opens the named configuration with seeded random weights made on the device:
+    ``random:NAME?seed=S&layers=L`` (``layers`` > 0 keeps that many of the configuration's layers;
+    every layer keeps its size)."""
+    q = [f"seed={int(seed)}"] + ([f"layers={int(layers)}"] if layers else [])
+    return f"{RANDOM_PREFIX}{name}?{'&'.join(q)}"
+
+
+def _parse_random(path: str):
+    from .config.presets import preset
+    body = path[len(RANDOM_PREFIX):]
+    name, _, query = body.partition("?")
+    args = {"seed": 0, "layers": 0}
+    for item in filter(None, query.split("&")):
+        k, _, v = item.partition("=")
+        if k not in args:
+            raise ValueError(f"gophonic_b200: unknown option '{k}' in {path} (seed, layers)")
+        try:
+            args[k] = int(v)
+        except ValueError:
+            raise ValueError(f"gophonic_b200: '{k}={v}' in {path} is not an integer") from None
+    try:
+        raw = preset(name)
+    except KeyError as e:
+        raise ErrUnknownFormat(f"gophonic_b200: {e.args[0]}") from None
+    if args["layers"] < 0 or args["layers"] > raw["num_hidden_layers"]:
+        raise ValueError(f"gophonic_b200: layers={args['layers']} of a configuration with {raw['num_hidden_layers']}")
+    if args["layers"]:
+        raw = dict(raw, num_hidden_layers=args["layers"])
+    return registry.config_class(registry.architecture_of(raw)).from_dict(raw), args["seed"]
+
+
+def _open_random(path: str, opts: Options) -> OpenedModel:
+    from .engine.model import Model
+    config, seed = _parse_random(path)
+    mode = "float32" if opts.Format == FormatF32 else "bfloat16"
+    model = Model.from_random(config, seed=seed, dtype=mode, device=opts.Device)
+    m = OpenedModel(model.spec.architecture, path)
+    m.model = model
+    Provide(m, TokensGenerator, lambda: TokenGenerator(model, opts, ()))
+    return Provide(m, ChatGeneratorLane, lambda: _open_chat(model, opts, path))
+
+
+Register(Format(Name="random-weights", Match=lambda path: path.startswith(RANDOM_PREFIX), Open=_open_random,
+                Provides=(TokensGenerator, ChatGeneratorLane)))

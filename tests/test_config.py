@@ -126,3 +126,38 @@ def test_stop_ids_come_from_the_model_folder(tmp_path):
     assert read_stop_ids(str(d)) == [151645, 151643]          # the generation config wins
     (d / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
     assert read_stop_ids(str(d)) == [7]                         # what is no id or list of ids is passed over
+
+
+def test_named_configurations_are_config_files_read_like_any_other():
+    from gophonic_b200 import registry
+    from gophonic_b200.api import ErrUnknownFormat, _parse_random, random_model_path
+    from gophonic_b200.config.presets import preset, preset_names
+    assert preset_names() == ["1.7b", "32b", "8b", "tinyA", "tinyB"]
+    for name in preset_names():
+        raw = preset(name)
+        cfg = registry.config_class(registry.architecture_of(raw)).from_dict(raw)
+        assert cfg.to_dict()["hidden_size"] == raw["hidden_size"]
+    big = preset("8b")
+    assert (big["num_hidden_layers"], big["hidden_size"], big["intermediate_size"], big["vocab_size"]) == (36, 4096, 12288, 151936)
+    cfg, seed = _parse_random(random_model_path("8b", seed=5, layers=2))
+    assert seed == 5 and cfg.num_hidden_layers == 2 and cfg.hidden_size == 4096
+    assert _parse_random("random:tinyB")[0].vocab_size == 1000
+    with pytest.raises(ErrUnknownFormat, match="no configuration named"):
+        _parse_random("random:70b")
+    with pytest.raises(ValueError, match="layers=99"):
+        _parse_random("random:8b?layers=99")
+    with pytest.raises(ValueError, match="unknown option"):
+        _parse_random("random:8b?depth=2")
+
+
+def test_command_line_refuses_what_it_cannot_run(tmp_path, capsys):
+    from gophonic_b200.__main__ import main
+    assert main([]) == 2
+    assert main(["-model", "x", "-random-config", "tinyA", "1"]) == 2
+    assert main(["-random-config", "tinyA"]) == 1 and "no prompt" in capsys.readouterr().err
+    assert main(["-model", "x", "1,b"]) == 2
+    assert main(["-model", str(tmp_path), "-write-model", str(tmp_path / "out"), "1"]) == 1
+    out = tmp_path / "written"
+    assert main(["-random-config", "tinyB", "-weights-seed", "9", "-layers", "1", "-write-model", str(out)]) == 0
+    from gophonic_b200.config import Qwen3Config
+    assert Qwen3Config.from_json(str(out)).num_hidden_layers == 1 and (out / "model.safetensors").exists()

@@ -153,6 +153,22 @@ def test_command_line(model_dirs, plain_models):
     assert bad.returncode == 1 and "gophonic_b200:" in bad.stderr
 
 
+def test_command_line_with_a_named_configuration_and_a_file_of_prompts(tmp_path):
+    """-random-config NAME -weights-seed S: the model the plain implementation makes from the same
+    configuration file and seed replies with the same tokens."""
+    from gophonic_b200.config.presets import preset
+    cfg = preset("tinyA")
+    w = P.random_weights(cfg, 3)
+    (tmp_path / "prompts.txt").write_text("5 6 7 8\n\n100,200\n")
+    proc = subprocess.run([sys.executable, "-m", "gophonic_b200", "-random-config", "tinyA", "-weights-seed", "3", "-format", "f32",
+                           "-max-tokens", "6", "-prompt-ids", str(tmp_path / "prompts.txt"), "3,9,27"],
+                          cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert [l["prompt"] for l in lines] == [[3, 9, 27], [5, 6, 7, 8], [100, 200]]
+    assert [l["tokens"] for l in lines] == [P.greedy_generate(l["prompt"], 6, cfg, w) for l in lines]
+
+
 def test_running_ahead_and_reading_every_token_first_give_the_same_replies(lanes, plain_models):
     """Many requests of random lengths, budgets and stop tokens, greedy and sampled, more than a batch
     holds: the loop that runs one step ahead (the engine's own) and the loop that reads every token
@@ -182,3 +198,107 @@ def test_running_ahead_and_reading_every_token_first_give_the_same_replies(lanes
     assert any(len(r) < o.MaxTokens for r, o in zip(ahead, options)), "some reply ended on a stop token"
     gen.engine.cache.check()
     assert gen.engine.cache.pages.held() == 0 and gen.engine.cache.slots.held() == 0
+
+
+# ---- the chat lane ------------------------------------------------------------------------------
+def plain_reply(ids, n_new, cfg, w, stop):
+    return P.greedy_generate(ids, n_new, cfg, w, stop_ids=stop)
+
+
+@pytest.mark.parametrize("name,fmt", [("A", "f32"), ("B", "f32"), ("D", "bf16")])
+def test_a_conversation_keeps_its_context_between_replies(model_dirs, plain_models, name, fmt):
+    """Lane "chat.Generator" over token ids: every reply equals a fresh greedy evaluation of the
+    whole conversation by the plain implementation (32-bit; in bfloat16 up to a near-tie), the
+    second reply evaluates only the tokens that are new, and a conversation cut back by Restore or
+    Truncate goes on from what the cache still shares with it."""
+    import gophonic_b200 as g
+    from gophonic_b200.chat import Template, User
+    cfg, w = plain_models[name]
+    m = g.Open(model_dirs[name], g.Options(Format=fmt, CacheTokens=1024))
+    assert g.Supports(m, g.ChatGeneratorLane)
+    chat = g.Lane(m, g.ChatGeneratorLane)
+    rng = np.random.default_rng(5)
+    V = cfg["vocab_size"]
+    stop = [int(rng.integers(0, V))]
+    chat.template = Template(header={User: [1, 2]}, end=[3], answer=[4, 5], stop=stop)
+    chat._loop.stop_ids = frozenset(stop)
+    exact = fmt == "f32"
+
+    def same(got, ids, n):
+        want = plain_reply(ids, n, cfg, w, stop)
+        if exact:
+            assert got == want
+        else:
+            k = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), min(len(got), len(want)))
+            assert k == len(want) == len(got) or k >= 1   # bfloat16 may leave the plain reply at a near-tie, not at once
+    s = chat.NewSession()
+    s.Add(User, rng.integers(0, V, size=70).tolist())
+    first = s.Reply(g.ChatOptions(MaxTokens=9))
+    same(first, s.ids[:s.reply_at], 9)
+    assert s.stats.kept == 0 and s.stats.prefill_tokens == s.reply_at
+    assert chat.engine.length(s.slot) == len(s.held) and s.held == s.ids[:len(s.held)]
+    # a second message: only what is new is evaluated
+    before = len(s.held)
+    s.Add(User, rng.integers(0, V, size=11).tolist())
+    second = s.Reply(g.ChatOptions(MaxTokens=6))
+    same(second, s.ids[:s.reply_at], 6)
+    assert s.stats.kept == min(before, s.reply_at - 1) and s.stats.prefill_tokens == s.reply_at - s.stats.kept < 25
+    # a message added speculatively, evaluated, dropped, replaced
+    mark = s.Checkpoint()
+    s.Add(User, [7, 8, 9, 10])
+    s.Prefill()
+    assert chat.engine.length(s.slot) == len(s.ids)
+    s.Restore(mark)
+    s.Add(User, [7, 8, 11])
+    third = s.Reply(g.ChatOptions(MaxTokens=5))
+    same(third, s.ids[:s.reply_at], 5)
+    assert s.stats.kept == mark + 4        # the frame's two tokens and 7, 8 were shared
+    # the reply is cut to its first two tokens, then the conversation goes on
+    if len(third) > 2:
+        s.Truncate(2)
+        assert s.ids[s.reply_at:] == third[:2] + [3]
+    s.Add(User, [12])
+    fourth = s.Reply(g.ChatOptions(MaxTokens=4))
+    same(fourth, s.ids[:s.reply_at], 4)
+    # a second session shares the model and the cache, not the slot
+    other = chat.NewSession()
+    other.Add(User, [5, 6, 7])
+    same(other.Reply(g.ChatOptions(MaxTokens=4)), other.ids[:other.reply_at], 4)
+    assert other.slot != s.slot
+    chat.engine.cache.check()
+    chat.Close()
+    assert chat.engine.cache.pages.held() == 0 and chat.engine.cache.slots.held() == 0
+    m.Close()
+
+
+def test_a_conversation_in_text(model_dirs, plain_models, tmp_path):
+    """A model folder with a tokenizer.json: messages are text, the frame is Qwen3's, the reply is
+    written piece by piece, and the ids are what the plain implementation generates from the framed
+    conversation."""
+    import shutil
+    import gophonic_b200 as g
+    from gophonic_b200.chat import User
+    from tests.test_tokenizer_chat import write_tokenizer
+    cfg, w = plain_models["A"]
+    d = str(tmp_path / "with_tokenizer")
+    shutil.copytree(model_dirs["A"], d)
+    vocab, base = write_tokenizer(d)
+    assert base + 4 <= cfg["vocab_size"]
+    m = g.Open(d, g.Options(Format="f32", CacheTokens=512))
+    chat = g.Lane(m, g.ChatGeneratorLane)
+    t = chat.tokenizer
+    s = chat.NewSession("be brief")
+    s.Add(User, "hello world")
+    heard = []
+
+    class Writer:
+        def write(self, text):
+            heard.append(text)
+    reply = s.Reply(g.ChatOptions(MaxTokens=12), writer=Writer())
+    framed = t.encode("<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nhello world<|im_end|>\n"
+                      "<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    assert s.ids[:s.reply_at] == framed
+    assert reply == P.greedy_generate(framed, 12, cfg, w, stop_ids=[base + 2, base])
+    assert "".join(heard) == t.decode(reply)
+    chat.Close()
+    m.Close()
