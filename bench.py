@@ -123,14 +123,14 @@ def time_decode(engine, sampler, batch, steps, warmup, torch, ops):
     out = {}
     try:
         for _ in range(warmup):
-            logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
+            logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)], borrow=True)
             tokens = sampler.select(logits, rows)
         torch.cuda.synchronize()
         l0 = ops.launches
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         for _ in range(steps):
-            logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
+            logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)], borrow=True)
             sampler.select_device(logits, rows)
         ev1.record()
         torch.cuda.synchronize()
@@ -286,12 +286,12 @@ def probe(name):
         ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
         slot, start = ints(list(range(nseq))), ints([i * q_len for i in range(nseq)])
         ql, kl = ints([q_len] * nseq), ints([kv_len] * nseq)
-        from gophonic_b200.engine.step import choose_splits
+        from gophonic_b200.parts.attention import choose_splits
         splits = 1 if q_len > 1 else choose_splits(nseq * kvh, kv_len)
         scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, d, splits), dtype=torch.float32, device=dev) if splits > 1 else None
 
         def fn():
-            ops.attention(q, out, k, v, table, 0, slot, start, ql, kl, nseq, q_len, heads, kvh, d, d ** -0.5, 0, splits, scratch)
+            ops.attention(q, out, k, v, table, slot, start, ql, kl, nseq, q_len, heads, kvh, d, d ** -0.5, 0, splits, scratch)
         if q_len == 1:
             work, unit = 2.0 * n_pages * kvh * 64 * d * 2, "GB/s"
         else:

@@ -103,7 +103,6 @@ class KVView:
     k: torch.Tensor            # [n_pages, kv_heads, 64, head_dim]
     v: torch.Tensor
     block_table: torch.Tensor  # [max_slots, max_pages_per_seq] int32
-    ring_pages: int
     writable: bool
     window: int
 
@@ -141,7 +140,11 @@ class Cache:
         self.slots = FreeList(self.max_slots, "slot")
         self._length = [0] * self.max_slots
         self._pages_of: List[List[int]] = [[] for _ in range(self.max_slots)]
-        self.block_table = torch.zeros((self.max_slots, self.max_pages_per_seq), dtype=torch.int32, device=self.device)
+        # One slot and one page beyond the pools belong to nobody: rows that only fill a step up to a
+        # captured size read and write there (``spare_slot``, whose first page is ``spare_page``).
+        self.spare_slot, self.spare_page = self.max_slots, self.n_pages
+        self.block_table = torch.zeros((self.max_slots + 1, self.max_pages_per_seq), dtype=torch.int32, device=self.device)
+        self.block_table[self.spare_slot, 0] = self.spare_page
 
         # groups
         self._kv_groups: Dict[Tuple[int, int, int], List[int]] = {}
@@ -171,13 +174,13 @@ class Cache:
         self._v: Dict[Tuple[int, int, int], torch.Tensor] = {}
         for key, planes in self._kv_groups.items():
             kvh, d, _w = key
-            shape = (len(planes), self.n_pages, kvh, PAGE, d)
+            shape = (len(planes), self.n_pages + 1, kvh, PAGE, d)
             self._k[key] = torch.zeros(shape, dtype=dtype, device=self.device)
             self._v[key] = torch.zeros(shape, dtype=dtype, device=self.device)
         self._state: Dict[Tuple[Tuple[int, ...], torch.dtype], torch.Tensor] = {}
         for key, planes in self._state_groups.items():
             shape, sdtype = key
-            self._state[key] = torch.zeros((len(planes), self.max_slots) + tuple(shape), dtype=sdtype, device=self.device)
+            self._state[key] = torch.zeros((len(planes), self.max_slots + 1) + tuple(shape), dtype=sdtype, device=self.device)
         self._ops = None
         self._stager = None
 
@@ -208,7 +211,7 @@ class Cache:
             return None
         kind, key, ordinal = self._plane[at]
         if kind == "kv":
-            return KVView(self._k[key][ordinal], self._v[key][ordinal], self.block_table, 0, writable, key[2])
+            return KVView(self._k[key][ordinal], self._v[key][ordinal], self.block_table, writable, key[2])
         return StateView(self._state[key][ordinal], writable)
 
     # ---- slots -------------------------------------------------------------------------

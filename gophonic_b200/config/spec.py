@@ -73,10 +73,16 @@ class SwiGLUSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement and the four parts it arranges.
+    """One layer of the pre-norm arrangement: the block kind and the four parts it arranges.
 
     ``prefix`` is the tensor-name prefix of the layer ("model.layers.3."); each part resolves its
-    tensors under the sub-prefix the block gives it.
+    tensors under the sub-prefix named here (the defaults are the names Qwen3 checkpoints use).
+
+    The model, the loader and the cache read only two fields of a layer's spec, ``block`` and
+    ``prefix``; everything else is between the spec and the block class registered under that
+    kind (``declare``, ``cache_request``, ``mixers``, ``prepare``, ``weight_bytes``, ``forward``).
+    A block with another arrangement (one shared norm, norms after the parts, two mixers) brings a
+    spec class of its own with those two fields.
     """
     prefix: str
     mixer: object

@@ -26,7 +26,6 @@ struct AttnParams {
     const void* v_plane;
     const int* block_table;
     int bt_stride;
-    int ring_pages;
     const int* seq_slot;
     const int* seq_q_start;
     const int* seq_q_len;
@@ -100,7 +99,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
     const int t_lo = lo_pos / 64, t_hi = hi_pos / 64;
 
     auto load_tile = [&](int t, int buf) {
-        int64_t page = page_of(bt, t * 64, p.ring_pages);
+        int64_t page = page_of(bt, t * 64);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
         load_page<HD>(Ks + buf * 64 * SD, kbase + off, tid, 128);
         load_page<HD>(Vs + buf * 64 * SD, vbase + off, tid, 128);
@@ -277,7 +276,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
 
     auto load_tile = [&](int i) {
         int t = my_lo + i;
-        int64_t page = page_of(bt, t * 64, p.ring_pages);
+        int64_t page = page_of(bt, t * 64);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
         bf16* st = KV + (i % DSTAGES) * STAGE;
         load_page<HD>(st, kbase + off, tid, 128);
@@ -487,7 +486,6 @@ int check(const AttnParams& p, const char* who) {
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if ((p.out_row_stride & 1) || ((uintptr_t)p.out & 3)) GB_REFUSE("%s: output rows must be 4-byte aligned", who);
-    if (p.ring_pages != 0) GB_REFUSE("%s: ring storage is not supported by this kernel", who);
     return 0;
 }
 

@@ -21,7 +21,6 @@ struct AttnParams {
     const void* v_plane;
     const int* block_table;
     int bt_stride;
-    int ring_pages;
     const int* seq_slot;
     const int* seq_q_start;
     const int* seq_q_len;
@@ -116,7 +115,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
             int j = warp * 8 + jj;
             int key = t * KT + j;
             if (key <= hi_pos) {
-                int64_t page = page_of(bt, key, p.ring_pages);
+                int64_t page = page_of(bt, key);
                 int64_t off = ((page * p.kv_heads + kvh) * GB_PAGE + (key % GB_PAGE)) * (int64_t)d;
                 const T* kp = (const T*)p.k_plane + off;
                 const T* vp = (const T*)p.v_plane + off;

@@ -33,7 +33,6 @@ struct AttnParams {
     const void* v_plane;
     const int* block_table;
     int bt_stride;
-    int ring_pages;
     const int* seq_slot;
     const int* seq_q_start;
     const int* seq_q_len;
@@ -564,7 +563,6 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (p.d != HD) GB_REFUSE("%s: head_dim %d; this kernel takes 128", who, p.d);
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("%s: %d heads over %d kv heads", who, p.heads, p.kv_heads);
     if (p.num_splits != 1) GB_REFUSE("%s: key splits are for single-token rows", who);
-    if (p.ring_pages != 0) GB_REFUSE("%s: ring storage is not supported by this kernel", who);
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if (((uintptr_t)p.out & 15) || (p.out_row_stride & 7)) GB_REFUSE("%s: output rows must be 16-byte aligned", who);

@@ -59,14 +59,8 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Physical location of token `pos` of the sequence whose block-table row is `bt`.
-// ring_pages > 0: the sequence keeps only that many pages and position p lives in page slot
-// (p / 64) % ring_pages (storage of a windowed group).
-__device__ __forceinline__ int64_t page_of(const int* __restrict__ bt, int pos, int ring_pages) {
-    int lp = pos / GB_PAGE;
-    if (ring_pages > 0) lp %= ring_pages;
-    return (int64_t)bt[lp];
-}
+// Physical page of token `pos` of the sequence whose block-table row is `bt`.
+__device__ __forceinline__ int64_t page_of(const int* __restrict__ bt, int pos) { return (int64_t)bt[pos / GB_PAGE]; }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

@@ -312,7 +312,6 @@ struct QkRopeParams {
     const int* seq_slot;
     const int* block_table;
     int bt_stride;
-    int ring_pages;
     void* k_plane;
     void* v_plane;
     int write_kv;
@@ -340,7 +339,7 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     } else {
         if (!p.write_kv) return;
         int slot = p.seq_slot[p.row_seq[r]];
-        int64_t page = page_of(p.block_table + (int64_t)slot * p.bt_stride, pos, p.ring_pages);
+        int64_t page = page_of(p.block_table + (int64_t)slot * p.bt_stride, pos);
         T* plane = (T*)(is_k ? p.k_plane : p.v_plane);
         dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)d;
     }
@@ -425,7 +424,7 @@ __global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) 
         }
 #pragma unroll
         for (int j = 0; j < ROPE_ROWS; j++) {
-            const int64_t page = page_of(p.block_table + (int64_t)slot[j] * p.bt_stride, pos[j], p.ring_pages);
+            const int64_t page = page_of(p.block_table + (int64_t)slot[j] * p.bt_stride, pos[j]);
             bf* plane = (bf*)(is_k ? p.k_plane : p.v_plane);
             dst[j] = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos[j] % GB_PAGE)) * (int64_t)128 + lane * 4;
         }

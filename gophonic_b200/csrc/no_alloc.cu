@@ -13,7 +13,6 @@ struct AttnParams {
     const void* v_plane;
     const int* block_table;
     int bt_stride;
-    int ring_pages;
     const int* seq_slot;
     const int* seq_q_start;
     const int* seq_q_len;

@@ -71,6 +71,9 @@ class Generator:
         self.stop_ids = frozenset(int(s) for s in stop_ids)
         self.page = page
         self.stats = GenerationStats()
+        # an engine that can lend its captured step's own output buffer is asked to: every step's
+        # logits are consumed by the sampler before the next step is issued
+        self._lend = {"borrow": True} if getattr(engine, "lends_logits", False) else {}
 
     # ---- planning ------------------------------------------------------------------------
     def _budget(self, prompt_len: int, options: Options) -> int:
@@ -148,7 +151,7 @@ class Generator:
                 self._begin(r, row)
                 live.append(r)
             # all prompts in one step
-            logits = self.engine.step([(r.slot, r.prompt) for r in live])
+            logits = self.engine.step([(r.slot, r.prompt) for r in live], **self._lend)
             self.stats.prefill_tokens += sum(len(r.prompt) for r in live)
             while True:
                 tokens = self.sampler.select(logits, [r.row for r in live])
@@ -163,7 +166,7 @@ class Generator:
                 if not live:
                     break
                 # one token each
-                logits = self.engine.step([(r.slot, [r.reply[-1]]) for r in live])
+                logits = self.engine.step([(r.slot, [r.reply[-1]]) for r in live], **self._lend)
                 for r in live:
                     r.fed.append(r.reply[-1])
                 self.stats.decode_steps += 1
@@ -180,7 +183,7 @@ class Generator:
             for row, r in enumerate(batch):
                 self._begin(r, row)
                 live.append(r)
-            logits = self.engine.step([(r.slot, r.prompt) for r in live])
+            logits = self.engine.step([(r.slot, r.prompt) for r in live], **self._lend)
             self.stats.prefill_tokens += sum(len(r.prompt) for r in live)
             drawn = self.sampler.select_device(logits, [r.row for r in live])   # tokens of `live`, on the device
             fetch = self.engine.fetch_tokens(drawn)
@@ -191,7 +194,7 @@ class Generator:
                 ahead = [(i, r) for i, r in enumerate(live) if r.finished is None and len(r.reply) + 1 < r.budget]
                 nxt = None
                 if ahead:
-                    logits = self.engine.step_from([r.slot for _, r in ahead], drawn, [i for i, _ in ahead])
+                    logits = self.engine.step_from([r.slot for _, r in ahead], drawn, [i for i, _ in ahead], **self._lend)
                     nxt_drawn = self.sampler.select_device(logits, [r.row for _, r in ahead])
                     nxt = ([r for _, r in ahead], nxt_drawn, self.engine.fetch_tokens(nxt_drawn))
                 # read and handle the tokens of the step before while the one just enqueued runs

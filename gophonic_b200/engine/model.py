@@ -91,9 +91,18 @@ class Model:
         out = []
         for entry in self.spec.schedule:
             layer = self.spec.layers[entry.layer]
-            req = registry.part_class("mixer", layer.mixer.kind).cache_request(layer.mixer)
-            out.append((req, entry.cache_of))
+            out.append((registry.part_class("block", layer.block).cache_request(layer), entry.cache_of))
         return out
+
+    def step_plans(self, nseq: int, max_q_len: int, max_kv_len: int, sm_count: int) -> Tuple:
+        """The launch plans of every mixer for a step of this shape, block by block: a hashable value
+        the engine keys its captured steps on without looking inside."""
+        return tuple(m.plan(nseq, max_q_len, max_kv_len, sm_count) for b in self.blocks for m in b.mixers())
+
+    def bind_plans(self, plans: Sequence) -> Dict[int, object]:
+        """``step_plans``' answer in the form ``StepBatch.plans`` takes: by mixer."""
+        mixers = [m for b in self.blocks for m in b.mixers()]
+        return {id(m): p for m, p in zip(mixers, plans)}
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None,
                   max_seq_tokens: Optional[int] = None) -> Cache:
@@ -102,7 +111,7 @@ class Model:
         cache = Cache(self.cache_requests(), max_tokens, self.rt.device, self.rt.act_dtype, max_slots, max_seq_tokens)
         capacity = cache.max_pages_per_seq * 64
         for b in self.blocks:
-            b.mixer.prepare(capacity)
+            b.prepare(capacity)
         return cache
 
     @property
@@ -114,10 +123,7 @@ class Model:
         """Bytes of weights a step reads once: every layer run's matrices and the head."""
         total = self.head.numel() * self.head.element_size()
         for entry in self.spec.schedule:
-            b = self.blocks[entry.layer]
-            for part in (b.mixer, b.feed_forward):
-                if hasattr(part, "weight_bytes"):
-                    total += part.weight_bytes()
+            total += self.blocks[entry.layer].weight_bytes()
         return total
 
     # ---- forward -------------------------------------------------------------------------

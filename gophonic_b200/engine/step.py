@@ -44,68 +44,25 @@ class StepBatch:
     seq_kv_len: torch.Tensor   # [nseq] keys visible to the sequence's last row (= its length after them)
     device: torch.device = None
     sm_count: int = 148
-    fixed_splits: Optional[int] = None
-    _scratch: Dict[Tuple[int, int, int], torch.Tensor] = field(default_factory=dict)
-    _chosen: Dict[Tuple[int, int], int] = field(default_factory=dict)   # (kv heads, page bytes) -> splits, per batch
+    # launch plans of the step's mixers, by the mixer's identity (``Mixer.plan``); a mixer that is
+    # not listed is asked when it first runs
+    plans: Dict[int, object] = field(default_factory=dict)
+    _workspaces: Dict[object, torch.Tensor] = field(default_factory=dict)
 
-    def decode_splits(self, heads: int, kv_heads: int, head_dim: int, elem_bytes: int = 2) -> Tuple[int, Optional[torch.Tensor]]:
-        """How many pieces single-token attention cuts each sequence's keys into, and the scratch
-        the pieces are merged through.  Few sequences with long contexts are cut so that every SM
-        has work; many sequences are not cut."""
-        if self.fixed_splits is not None:
-            splits = self.fixed_splits
-        else:
-            page_bytes = 2 * 64 * head_dim * elem_bytes
-            splits = self._chosen.get((kv_heads, page_bytes))
-            if splits is None:   # every attention layer of a step asks; the answer is the batch's
-                splits = self._chosen[(kv_heads, page_bytes)] = choose_splits(self.nseq * kv_heads, self.max_kv_len, self.sm_count, page_bytes)
-        if splits <= 1:
-            return 1, None
-        key = (heads, head_dim, splits)
-        if key not in self._scratch:
-            n = self.nseq * heads * splits * (head_dim + 2)
-            self._scratch[key] = torch.empty(n, dtype=torch.float32, device=self.device)
-        return splits, self._scratch[key]
+    def plan_for(self, part):
+        """The launch plan of ``part`` for this step (asked once per step and part)."""
+        key = id(part)
+        if key not in self.plans:
+            self.plans[key] = part.plan(self.nseq, self.max_q_len, self.max_kv_len, self.sm_count)
+        return self.plans[key]
 
-
-def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: int = 32768) -> int:
-    """How many pieces single-token attention cuts each sequence's keys into.  ``units`` =
-    (sequence, kv head) pairs, each one CTA per piece; ``page_bytes`` = keys and values of one kv
-    head for one page of 64 tokens.
-
-    The choice minimises a small model of the kernel's time that was fitted to measurements at 1
-    to 64 sequences of 4096 keys: two CTAs fit on an SM and run in waves; a wave takes the longer
-    of its bytes at the memory bandwidth and of one CTA's own pace (a little over a microsecond a page),
-    so a thin last wave costs as much as a full one unless its CTAs are short; cutting the keys
-    costs the merge kernel and the traffic of the partial results.  A piece keeps at least 256
-    keys.
-    """
-    units = max(1, units)
-    pages = max(1, (max_kv_len + 63) // 64)
-    most = max(1, min(32, max_kv_len // 256))
-    slots = 2 * sm_count
-    bytes_per_us = 6.0e6
-    page_us = 0.575 + 0.575 * page_bytes / 32768.0
-    if 4 * units > 9 * slots:
-        # more than two and a quarter waves uncut: the CTAs no longer run in step and a thin last
-        # wave costs little (112 sequences x 8 kv heads ran 2 % faster uncut than in 4 or 8 pieces)
-        return 1
-    best, best_t = 1, None
-    for s in range(1, most + 1):
-        p = (pages + s - 1) // s
-        ctas = units * s
-        full, rest = divmod(ctas, slots)
-        pace = p * page_us + 3.0
-        t = full * max(slots * p * page_bytes / bytes_per_us, pace)
-        if rest:
-            t += max(rest * p * page_bytes / bytes_per_us, pace)
-        if s > 1:
-            # the merge kernel, and the partial results (about four heads a unit, 130 floats each)
-            # written and read back
-            t += 5.0 + 0.15 * s + units * s * 4 * 1040 / 3.0e6
-        if best_t is None or t < 0.99 * best_t:
-            best, best_t = s, t
-    return best
+    def workspace(self, key, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """Scratch memory of this step: parts that ask with the same ``key`` share one buffer (they run
+        one after the other on the stream), and a captured step keeps its buffers for its replays."""
+        t = self._workspaces.get(key)
+        if t is None or t.numel() < numel or t.dtype != dtype:
+            t = self._workspaces[key] = torch.empty(numel, dtype=dtype, device=self.device)
+        return t
 
 
 class HostStager:
@@ -227,11 +184,6 @@ class Engine:
         if use_graphs and model.capturable:
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self, max_graph_batch)
-        # kv heads of the widest attention group: how many CTAs a sequence gives single-token attention
-        kv_groups = [g for g in self.cache.groups() if g["kind"] == "kv"]
-        self._kv_heads_hint = max([g["kv_heads"] for g in kv_groups] or [1])
-        # keys and values of one kv head for one page of 64 tokens, in the widest group
-        self._page_bytes_hint = max([g["bytes_per_token"] // (len(g["planes"]) * g["kv_heads"]) * 64 for g in kv_groups] or [32768])
 
     # ---- slots ---------------------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -309,11 +261,19 @@ class Engine:
                     if not 0 <= int(w) < len(toks):
                         raise StepError(f"entry {i} (slot {slot}): wanted place {w} is outside its {len(toks)} tokens")
 
+    # ``step(..., borrow=True)`` may return the output buffer of a replayed graph (see ``step``)
+    lends_logits = True
+
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+             want: Optional[Sequence[Sequence[int]]] = None, borrow: bool = False) -> Optional[torch.Tensor]:
         """Run ``entries = [(slot, tokens), ...]``; return fp32 logits [sum(len(w) for w in want), vocab]
         in the order of the entries and of each want list.  ``want=None`` asks for the last place
-        of every entry."""
+        of every entry.
+
+        The tensor returned is the caller's to keep.  With ``borrow`` it may instead be the output
+        buffer of a replayed CUDA graph, which the next step of the same shape overwrites: for a
+        caller that consumes the logits before it steps again (the generation loop), this saves a
+        copy."""
         self.validate(entries, want)
         if want is None:
             want = [[len(toks) - 1] for _, toks in entries]
@@ -332,6 +292,8 @@ class Engine:
         if (single and self.graphs is not None and total_rows <= self.graphs.max_batch
                 and want_rows == list(range(total_rows))):
             logits = self._graph_pass(entries)
+            if not borrow:
+                logits = logits.clone()
         elif total_rows <= self.max_rows_per_pass:
             pieces = [(slot, list(toks), self.cache.length(slot)) for slot, toks in entries]
             logits = self._pass(pieces, want_rows)
@@ -340,11 +302,12 @@ class Engine:
         self.cache.commit(grow)
         return logits
 
-    def step_from(self, slots: Sequence[int], source: torch.Tensor, positions: Sequence[int]) -> torch.Tensor:
+    def step_from(self, slots: Sequence[int], source: torch.Tensor, positions: Sequence[int],
+                  borrow: bool = False) -> torch.Tensor:
         """One token each: sequence ``slots[i]`` goes on by ``source[positions[i]]``, where ``source``
         is a device int32 tensor (what the sampler left for the step before).  The host need not
         have read the tokens, so this step can be enqueued while the last one still runs.  Returns
-        fp32 logits [len(slots), vocab]."""
+        fp32 logits [len(slots), vocab]; ``borrow`` as for ``step``."""
         if source.dtype != torch.int32 or source.dim() != 1 or source.device != self.device:
             raise StepError("step_from: the token source must be a 1-d int32 tensor on the engine's device")
         if len(slots) != len(positions) or not slots:
@@ -361,6 +324,8 @@ class Engine:
         n = len(entries)
         if self.graphs is not None and n <= self.graphs.max_batch:
             logits = self._graph_pass(entries, source)
+            if not borrow:
+                logits = logits.clone()
         elif n <= self.max_rows_per_pass:
             pieces = [(slot, toks, self.cache.length(slot)) for slot, toks in entries]
             logits = self._pass(pieces, list(range(n)), source)
@@ -392,10 +357,14 @@ class Engine:
         return self.model.forward(batch, self.cache, want_dev)
 
     def _graph_pass(self, entries, source: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """One token each, every row wanted: replay the captured step."""
+        """One token each, every row wanted: replay the captured step.  Steps are captured at a few
+        batch sizes only (every size up to 8, then 12, 16, 24, ... 128): a batch between two of them
+        is filled up with rows that read and write the cache's spare slot and whose logits nobody
+        sees, so that a batch which shrinks one sequence at a time does not capture a graph at every
+        size."""
         n = len(entries)
         firsts = [self.cache.length(slot) for slot, _ in entries]
-        g = self.graphs.get(n, max(firsts) + 1, self._kv_heads_hint, self._page_bytes_hint)
+        g = self.graphs.get(n, max(firsts) + 1)
         if g.logits is None:
             # the capture runs the step's kernels on the graph's own input buffer: fill it first
             self._fill_graph_meta(g, entries, firsts)
@@ -407,21 +376,28 @@ class Engine:
         if source is not None:
             self.model.rt.ops.gather_tokens(g.meta[:n], source)  # the ids section held positions
         self.passes += 1
-        return g.replay()
+        return g.replay()[:n]
 
     def _fill_graph_meta(self, g, entries, firsts) -> None:
-        n = len(entries)
+        n, nb = len(entries), g.nseq
+        spare = self.cache.spare_slot
 
         def fill(buf):
             for i, ((slot, toks), first) in enumerate(zip(entries, firsts)):
                 buf[i] = toks[0]
-                buf[n + i] = first
-                buf[2 * n + i] = i
-                buf[3 * n + i] = slot
-                buf[4 * n + i] = i
-                buf[5 * n + i] = 1
-                buf[6 * n + i] = first + 1
-                buf[7 * n + i] = i
+                buf[nb + i] = first
+                buf[3 * nb + i] = slot
+                buf[6 * nb + i] = first + 1
+            for i in range(n, nb):      # filler rows: token 0 at places of their own in the spare page
+                buf[i] = 0
+                buf[nb + i] = (i - n) % 64
+                buf[3 * nb + i] = spare
+                buf[6 * nb + i] = (i - n) % 64 + 1
+            for i in range(nb):
+                buf[2 * nb + i] = i
+                buf[4 * nb + i] = i
+                buf[5 * nb + i] = 1
+                buf[7 * nb + i] = i
         self.stager.upload_into(g.meta, fill)
 
     def _chunked(self, entries, starts, want_rows) -> Optional[torch.Tensor]:

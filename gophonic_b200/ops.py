@@ -373,7 +373,7 @@ class _QkRopeParams(Structure):
         ("qkv", c_void_p), ("row_stride", c_int64), ("q_w", c_void_p), ("k_w", c_void_p), ("eps", c_float),
         ("cos_t", c_void_p), ("sin_t", c_void_p), ("rot", c_int), ("table_positions", c_int),
         ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p), ("block_table", c_void_p),
-        ("bt_stride", c_int), ("ring_pages", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
+        ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
         ("write_kv", c_int), ("rows", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
     ]
 
@@ -382,7 +382,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim
                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
                           row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
-                          block_table: torch.Tensor, ring_pages: int,
+                          block_table: torch.Tensor,
                           k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool) -> None:
     """Per-head RMSNorm of q and k, rotary embedding of both, q in place, k and v into the cache."""
     _need(qkv, "qkv", dim=2)
@@ -413,7 +413,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim
                       0 if k_weight is None else k_weight.data_ptr(), eps,
                       0 if cos is None else cos.data_ptr(), 0 if sin is None else sin.data_ptr(), rotary_dim,
                       table_positions, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
-                      block_table.data_ptr(), block_table.stride(0), ring_pages,
+                      block_table.data_ptr(), block_table.stride(0),
                       0 if k_plane is None else k_plane.data_ptr(), 0 if v_plane is None else v_plane.data_ptr(),
                       1 if write_kv else 0, rows, heads, kv_heads, head_dim)
     _check(_lib.gb_qk_norm_rope_kv_write(byref(p), _code(qkv.dtype), _stream()))
@@ -423,7 +423,7 @@ class _AttnParams(Structure):
     _fields_ = [
         ("q", c_void_p), ("q_row_stride", c_int64), ("out", c_void_p), ("out_row_stride", c_int64),
         ("k_plane", c_void_p), ("v_plane", c_void_p), ("block_table", c_void_p), ("bt_stride", c_int),
-        ("ring_pages", c_int), ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
+        ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
         ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
     ]
@@ -439,7 +439,7 @@ def attention_scratch_floats(nseq: int, heads: int, head_dim: int, num_splits: i
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
-              block_table: torch.Tensor, ring_pages: int, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+              block_table: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
               seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
               heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
               num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto") -> str:
@@ -466,12 +466,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
         if scratch.numel() < attention_scratch_floats(nseq, heads, head_dim, num_splits):
             raise KernelError("attention: scratch is too small")
     p = _AttnParams(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_plane.data_ptr(), v_plane.data_ptr(),
-                    block_table.data_ptr(), block_table.stride(0), ring_pages, seq_slot.data_ptr(),
+                    block_table.data_ptr(), block_table.stride(0), seq_slot.data_ptr(),
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr())
     if algo == "auto":
         algo = "simt"
-        if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and (head_dim <= 128 or head_dim == 256) and ring_pages == 0:
+        if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and (head_dim <= 128 or head_dim == 256):
             if max_q_len == 1:
                 algo = "decode_mma"
             elif (max_q_len >= TC5_ATTENTION_MIN_ROWS and head_dim == 128

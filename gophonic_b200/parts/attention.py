@@ -19,6 +19,46 @@ from .. import registry
 from .base import KVRequest, Mixer, Runtime, TensorDecl
 
 
+def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: int = 32768) -> int:
+    """How many pieces single-token attention cuts each sequence's keys into.  ``units`` =
+    (sequence, kv head) pairs, each one CTA per piece; ``page_bytes`` = keys and values of one kv
+    head for one page of 64 tokens.
+
+    The choice minimises a small model of the kernel's time that was fitted to measurements at 1
+    to 64 sequences of 4096 keys: two CTAs fit on an SM and run in waves; a wave takes the longer
+    of its bytes at the memory bandwidth and of one CTA's own pace (a little over a microsecond a page),
+    so a thin last wave costs as much as a full one unless its CTAs are short; cutting the keys
+    costs the merge kernel and the traffic of the partial results.  A piece keeps at least 256
+    keys.
+    """
+    units = max(1, units)
+    pages = max(1, (max_kv_len + 63) // 64)
+    most = max(1, min(32, max_kv_len // 256))
+    slots = 2 * sm_count
+    bytes_per_us = 6.0e6
+    page_us = 0.575 + 0.575 * page_bytes / 32768.0
+    if 4 * units > 9 * slots:
+        # more than two and a quarter waves uncut: the CTAs no longer run in step and a thin last
+        # wave costs little (112 sequences x 8 kv heads ran 2 % faster uncut than in 4 or 8 pieces)
+        return 1
+    best, best_t = 1, None
+    for s in range(1, most + 1):
+        p = (pages + s - 1) // s
+        ctas = units * s
+        full, rest = divmod(ctas, slots)
+        pace = p * page_us + 3.0
+        t = full * max(slots * p * page_bytes / bytes_per_us, pace)
+        if rest:
+            t += max(rest * p * page_bytes / bytes_per_us, pace)
+        if s > 1:
+            # the merge kernel, and the partial results (about four heads a unit, 130 floats each)
+            # written and read back
+            t += 5.0 + 0.15 * s + units * s * 4 * 1040 / 3.0e6
+        if best_t is None or t < 0.99 * best_t:
+            best, best_t = s, t
+    return best
+
+
 class Attention(Mixer):
     capturable = True
 
@@ -65,6 +105,15 @@ class Attention(Mixer):
     def prepare(self, capacity: int) -> None:
         self.position.prepare(capacity)
 
+    def plan(self, nseq: int, max_q_len: int, max_kv_len: int, sm_count: int):
+        """Into how many pieces the keys of each sequence are cut: only single-token steps cut them
+        (few sequences with long contexts would otherwise leave most SMs idle)."""
+        if max_q_len != 1:
+            return 1
+        elem = 4 if self.rt.is_fp32 else 2
+        page_bytes = 2 * 64 * self.spec.head_dim * elem     # keys and values of one kv head for one page
+        return choose_splits(nseq * self.spec.kv_heads, max_kv_len, sm_count, page_bytes)
+
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
         self.rt.ops.gemm(self._context(batch, x, cache), self.o, out)
 
@@ -89,12 +138,13 @@ class Attention(Mixer):
         cos, sin, rot = self.position.kernel_args()
         ops.qk_norm_rope_kv_write(qkv, s.heads, s.kv_heads, s.head_dim, self.q_norm, self.k_norm, self.eps,
                                   cos, sin, rot, batch.row_pos, batch.row_seq, batch.seq_slot,
-                                  cache.block_table, cache.ring_pages, cache.k, cache.v, cache.writable)
+                                  cache.block_table, cache.k, cache.v, cache.writable)
         ctx = torch.empty((rows, self.q_dim), dtype=x.dtype, device=x.device)
-        splits, scratch = 1, None
-        if batch.max_q_len == 1:
-            splits, scratch = batch.decode_splits(s.heads, s.kv_heads, s.head_dim, cache.k.element_size())
-        ops.attention(qkv[:, :self.q_dim], ctx, cache.k, cache.v, cache.block_table, cache.ring_pages,
+        splits, scratch = int(batch.plan_for(self) or 1), None
+        if splits > 1:   # partial results of the pieces, merged by a second kernel
+            scratch = batch.workspace(("attention key splits", s.heads, s.head_dim, splits),
+                                      ops.attention_scratch_floats(batch.nseq, s.heads, s.head_dim, splits))
+        ops.attention(qkv[:, :self.q_dim], ctx, cache.k, cache.v, cache.block_table,
                       batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len, batch.nseq,
                       batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),
                       splits, scratch)

@@ -108,6 +108,15 @@ class Mixer(Part):
     def prepare(self, capacity: int) -> None:
         pass
 
+    def plan(self, nseq: int, max_q_len: int, max_kv_len: int, sm_count: int):
+        """How this mixer will launch a step of ``nseq`` sequences that bring at most ``max_q_len``
+        rows each and see at most ``max_kv_len`` keys: any hashable value, or None if the launch
+        does not depend on these numbers.  The engine does not look inside: it asks once per step,
+        hands the answer back through ``batch.plan_for(self)``, and keys its captured steps on the
+        answers of all mixers, so a step is replayed only with the launch shape it was captured
+        with.  Scratch memory that the plan calls for comes from ``batch.workspace(key, n)``."""
+        return None
+
     def adds_in_place(self, rows: int) -> bool:
         """True if, for a step of ``rows`` rows, ``forward_into(batch, x, h, cache)`` is the faster
         way: the part then adds its output to the fp32 residual ``h`` itself (in the epilogue of its

@@ -46,6 +46,21 @@ class PreNormBlock(Part):
         self.feed_forward = registry.part_class("feed_forward", layer.feed_forward.kind)(
             layer.feed_forward, p + layer.feed_forward_prefix, tensors, runtime)
 
+    # What a model asks of a block, whatever its arrangement: the cache its runs need, tables for a
+    # capacity, its mixers' launch plans, the weight bytes of one run, and whether it can be captured.
+    @classmethod
+    def cache_request(cls, layer):
+        return registry.part_class("mixer", layer.mixer.kind).cache_request(layer.mixer)
+
+    def prepare(self, capacity: int) -> None:
+        self.mixer.prepare(capacity)
+
+    def mixers(self) -> List[Part]:
+        return [self.mixer]
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward) if hasattr(p, "weight_bytes"))
+
     @property
     def capturable(self) -> bool:
         return all(p.capturable for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward))

@@ -93,13 +93,14 @@ def test_groups_have_storage_of_their_own_and_shared_planes():
     kinds = sorted((g["kind"], tuple(g["planes"])) for g in c.groups())
     assert kinds == [("kv", (0, 2)), ("kv", (1,)), ("kv", (6,)), ("state", (3,))]
     v0, v1, v2, v5 = c.view(0), c.view(1), c.view(2), c.view(5)
-    assert v0.k.shape == (c.n_pages, 2, PAGE, 16) and c.view(6).k.shape == (c.n_pages, 1, PAGE, 32)
+    # one page and one slot beyond the pools are nobody's: rows that fill a captured step up use them
+    assert v0.k.shape == (c.n_pages + 1, 2, PAGE, 16) and c.view(6).k.shape == (c.n_pages + 1, 1, PAGE, 32)
     assert v0.k.data_ptr() != v2.k.data_ptr() != v1.k.data_ptr()
     assert v1.window == 128 and v0.window == 0
     assert v5.k.data_ptr() == v0.k.data_ptr() and not v5.writable and v0.writable
     assert c.view(4) is None
     st = c.view(3)
-    assert st.state.shape == (c.max_slots, 4, 3)
+    assert st.state.shape == (c.max_slots + 1, 4, 3) and c.block_table[c.spare_slot, 0] == c.spare_page == c.n_pages
     s = c.alloc_slot()
     st.state[s] += 5
     c.free_slot(s)
@@ -154,7 +155,7 @@ def test_key_splits_of_single_token_attention():
     """The choice of how many pieces a sequence's keys are cut into: short contexts are not cut, a
     piece keeps at least 256 keys, few sequences are cut until every SM has work, and a batch
     that fills the machine a little more than once is cut so that its last wave is not thin."""
-    from gophonic_b200.engine import choose_splits
+    from gophonic_b200.parts.attention import choose_splits
     for units in (1, 8, 64, 300, 512, 4000):
         assert choose_splits(units, 1) == 1
         assert choose_splits(units, 255) == 1

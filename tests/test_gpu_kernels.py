@@ -289,7 +289,7 @@ def test_qk_norm_rope_kv_write(ops, dtype, heads, kvh, d, rot, qk_norm):
         c, s = P.rope_tables(np.arange(256), rot, theta)
         cos, sin = (torch.tensor(x, dtype=torch.float32, device=DEV) for x in (c, s))
     ops.qk_norm_rope_kv_write(qkv, heads, kvh, d, qw, kw, eps, cos, sin, rot, row_pos, row_seq, seq_slot,
-                              table, 0, k_plane, v_plane, True)
+                              table, k_plane, v_plane, True)
     # reference in float64 from the inputs
     x = qkv0.double().cpu().numpy()
     q = x[:, :heads * d].reshape(rows, heads, d)
@@ -320,7 +320,7 @@ def test_qk_norm_rope_kv_write(ops, dtype, heads, kvh, d, rot, qk_norm):
     # a run that reads another run's cache writes nothing
     qkv2, k2, v2 = qkv0.clone(), k0.clone(), v0.clone()
     ops.qk_norm_rope_kv_write(qkv2, heads, kvh, d, qw, kw, eps, cos, sin, rot, row_pos, row_seq, seq_slot,
-                              table, 0, k2, v2, False)
+                              table, k2, v2, False)
     assert torch.equal(k2, k0) and torch.equal(v2, v0) and torch.equal(qkv2[:, :heads * d], qkv[:, :heads * d])
 
 
@@ -365,7 +365,7 @@ def attention_case(ops, dtype, heads, kvh, d, q_lens, kv_lens, window=0, splits=
     scratch = None
     if splits > 1:
         scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, d, splits), dtype=torch.float32, device=DEV)
-    used = ops.attention(q, out, k_plane, v_plane, table, 0, mk(slots), mk(starts), mk(q_lens), mk(kv_lens), nseq,
+    used = ops.attention(q, out, k_plane, v_plane, table, mk(slots), mk(starts), mk(q_lens), mk(kv_lens), nseq,
                          max(q_lens), heads, kvh, d, scale, window, splits, scratch, algo=algo)
     ref = attention_reference(q, k_plane, v_plane, table, slots, q_lens, kv_lens, heads, kvh, d, scale, window)
     return out, ref, used
@@ -416,7 +416,7 @@ def test_attention_long_prompt_starts_its_ctas_kv_head_by_kv_head(ops):
     outs = {}
     for algo in ("prefill_tc5", "prefill_mma"):
         out = torch.full((n, heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-        used = ops.attention(q, out, k_plane, v_plane, table, 0, mk([0]), mk([0]), mk([n]), mk([n]), 1, n, heads, kvh, d,
+        used = ops.attention(q, out, k_plane, v_plane, table, mk([0]), mk([0]), mk([n]), mk([n]), 1, n, heads, kvh, d,
                              d ** -0.5, 0, 1, None, algo=algo)
         assert used == algo
         outs[algo] = out.float()

@@ -384,6 +384,45 @@ def test_a_sequence_rewound_and_continued_equals_a_fresh_one(engines, references
     assert eng.cache.pages.held() == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_that_shrinks_is_replayed_at_a_few_captured_sizes(model_dirs, references, plain_models, dtype):
+    """Thirteen sequences decode together and end one after the other.  Steps of 13 to 9 sequences
+    are replayed from graphs captured at 16 and 12, filled up with rows that live in the cache's
+    spare slot; the logits of the real rows are the plain implementation's, the spare rows touch no
+    real page, and a step's logits stay the caller's own when the next step runs (only a caller
+    that asks to borrow gets the graph's buffer)."""
+    from gophonic_b200.engine import Engine, Model
+    from gophonic_b200.engine.graphs import captured_size
+    assert [captured_size(n) for n in (1, 8, 9, 12, 13, 17, 33, 64, 65, 128)] == [1, 8, 12, 12, 16, 24, 48, 64, 96, 128]
+    cfg, _ = plain_models["B"]
+    eng = Engine(Model.from_dir(model_dirs["B"], dtype=dtype), max_tokens=4096)
+    reqs = list(requests_for(cfg, 61, [3 + 5 * i for i in range(13)]).values())
+    extra = 14
+    toks = [r + requests_for(cfg, 70 + i, [extra])["r0"] for i, r in enumerate(reqs)]
+    slots = [eng.new_sequence() for _ in reqs]
+    eng.step(list(zip(slots, reqs)))
+    live = list(range(13))
+    kept = []
+    for step in range(extra):
+        out = eng.step([(slots[i], [toks[i][len(reqs[i]) + step]]) for i in live])
+        kept.append((list(live), out))
+        if step < 12:
+            eng.end_sequence(slots[live.pop()])       # the batch shrinks by one sequence a step
+    sizes = sorted({k[0] for k in eng.graphs.graphs})
+    assert sizes == [1, 2, 3, 4, 5, 6, 7, 8, 12, 16], sizes
+    for step, (who, out) in enumerate(kept):
+        out = out.cpu().numpy()       # read after all later steps ran: nothing overwrote it
+        for j, i in enumerate(who):
+            ref = references("B", toks[i])[len(reqs[i]) + step]
+            assert float(np.max(np.abs(out[j] - ref)) / np.max(np.abs(ref))) < TOL[dtype], (step, i)
+    a = eng.step([(slots[0], [1])], borrow=True)
+    b = eng.step([(slots[0], [2])], borrow=True)
+    assert a.data_ptr() == b.data_ptr()               # a borrowed result is the graph's own buffer
+    eng.end_sequence(slots[0])
+    eng.cache.check()
+    assert eng.cache.pages.held() == 0
+
+
 def test_where_a_sequence_lies_in_the_cache_changes_nothing(engines, plain_models):
     eng = engines("A", "float32", 1024)
     cfg, _ = plain_models["A"]

@@ -24,7 +24,7 @@ DEV = "cuda:0"
 class Params(Structure):
     _fields_ = [("q", c_void_p), ("q_row_stride", c_int64), ("out", c_void_p), ("out_row_stride", c_int64),
                 ("k_plane", c_void_p), ("v_plane", c_void_p), ("block_table", c_void_p), ("bt_stride", c_int),
-                ("ring_pages", c_int), ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
+                ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
                 ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
                 ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p)]
 
