@@ -25,7 +25,9 @@
 // Set-up.  The first call on each device looks up the array's device address
 // (cudaGetSymbolAddress, with that device current) and keeps it; make that first call before any
 // stream capture begins.  No call allocates or frees: not through the CUDA runtime and not
-// through any library.
+// through any library.  The address is kept in a plain per-device table without a lock: two host
+// threads that make the first call on one device at the same time both look the address up and
+// both store the same value, which is harmless.
 //
 // Sharing.  All calls on a device use the same array, and it keeps what the last call left in
 // it.  Nothing in it has to start at zero: every slot that the merge reads is written first by

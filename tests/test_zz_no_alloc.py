@@ -51,7 +51,7 @@ def case(dtype, heads, kvh, d, kv_lens, splits, seed):
     meta = dict(slot=ints(list(range(nseq))), start=ints(list(range(nseq))), qlen=ints([1] * nseq), kvlen=ints(kv_lens))
     out = torch.full((nseq, heads * d), float("nan"), dtype=dtype, device=DEV)
     p = Params(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k.data_ptr(), v.data_ptr(), table.data_ptr(),
-               table.stride(0), 0, meta["slot"].data_ptr(), meta["start"].data_ptr(), meta["qlen"].data_ptr(),
+               table.stride(0), meta["slot"].data_ptr(), meta["start"].data_ptr(), meta["qlen"].data_ptr(),
                meta["kvlen"].data_ptr(), nseq, heads, kvh, d, 1, 1.0 / math.sqrt(d), 0, splits, 0)
     keep = (q, k, v, table, meta)
     return p, out, keep
