@@ -32,7 +32,6 @@ SOURCES = [
     "elementwise.cu",
     "cache_fill.cu",
     "gemm_simt.cu",
-    "gemm_mma.cu",
     "gemm_skinny.cu",
     "gemm_tc5.cu",
     "gemm_tc5_decode.cu",

@@ -261,7 +261,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     bfloat16 activations with bfloat16 weights go to the tensor-core kernels (``gemm_algo``): up to
     8 rows the fragment-streaming kernel, up to 128 (256 for narrow outputs with a long K) the
     tcgen05 decode kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs
-    two SMs on a tile; mma.sync tiles only when asked for by name.  Everything else,
+    two SMs on a tile.  Everything else,
     and operands whose rows are not 16-byte aligned, goes to the fp32 CUDA-core kernel.  float32
     operands never touch a tensor core.
     """
@@ -287,9 +287,6 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     if algo == "skinny":
         _check(_lib.gb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                    c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
-    elif algo == "mma":
-        _check(_lib.gb_gemm_mma(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
-                                c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
     elif algo == "tc5":
         _check(_lib.gb_gemm_tc5(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                 c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))

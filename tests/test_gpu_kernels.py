@@ -137,7 +137,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
     assert torch.equal(one[0], full[67])
 
 
-@pytest.mark.parametrize("algo", ["skinny", "mma", "tc5", "tc5_pair", "tc5_decode"])
+@pytest.mark.parametrize("algo", ["skinny", "tc5", "tc5_pair", "tc5_decode"])
 @pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (100, 1536, 2048), (128, 200, 8200), (256, 4096, 520),
                                             (300, 1000, 512), (2048, 512, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
