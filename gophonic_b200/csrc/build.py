@@ -33,6 +33,7 @@ SOURCES = [
     "cache_fill.cu",
     "gemm_simt.cu",
     "gemm_skinny.cu",
+    "gemm_skinny_fold.cu",
     "gemm_tc5.cu",
     "gemm_tc5_decode.cu",
     "attention_simt.cu",

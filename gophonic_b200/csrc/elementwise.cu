@@ -22,26 +22,51 @@ GB_API int gb_abi_version() { return 1; }
 
 // ------------------------------------------------------------------------------------------
 // embedding: h[r, :] = float(table[ids[r], :])      (internal/qwen3lm/evaluator.go:594-599)
+// With `stats`, the sum of squares of each row is left in stats[row * stats_stride] (one partial sum
+// a row, taken in a fixed order), and with `next_w` also xn_out[row] = bf16(row * next_w): the first
+// norm's output but for the row factor, for a product that applies that factor itself.
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids, int hidden,
-                                    int vocab, float* __restrict__ out) {
+                                    int vocab, float* __restrict__ out, float* __restrict__ stats, int64_t stats_stride,
+                                    const float* __restrict__ next_w, __nv_bfloat16* __restrict__ xn_out, int64_t ldxn) {
+    __shared__ float warp_part[8];
     int r = blockIdx.x;
     int id = ids[r];
     // ids are validated on the host; an id outside the table reads row 0 rather than faulting.
     if (id < 0 || id >= vocab) id = 0;
     const T* src = table + (int64_t)id * hidden;
     float* dst = out + (int64_t)r * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_f32<T>(src[i]);
+        dst[i] = v;
+        ss += v * v;
+        if (next_w != nullptr) xn_out[(int64_t)r * ldxn + i] = __float2bfloat16_rn(v * next_w[i]);
+    }
+    if (stats == nullptr) return;
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) t += warp_part[i];
+        stats[(int64_t)r * stats_stride] = t;
+    }
 }
 
 GB_API int gb_embed_gather(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab,
-                           float* out, cudaStream_t stream) {
+                           float* out, float* stats, int64_t stats_stride, const float* next_w, void* xn_out, int64_t ldxn,
+                           cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) GB_REFUSE("embed_gather: hidden %d, vocab %d", hidden, vocab);
+    if (next_w && (!xn_out || ldxn < hidden)) GB_REFUSE("embed_gather: a norm weight is given without room for its %d-wide rows", hidden);
     if (table_dtype == GB_F32)
-        embed_gather_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, hidden, vocab, out);
+        embed_gather_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, hidden, vocab, out, stats, stats_stride, next_w,
+                                                             (__nv_bfloat16*)xn_out, ldxn);
     else if (table_dtype == GB_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, hidden, vocab, out);
+        embed_gather_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, hidden, vocab, out, stats, stats_stride,
+                                                                     next_w, (__nv_bfloat16*)xn_out, ldxn);
     else
         GB_REFUSE("embed_gather: unknown table dtype %d", table_dtype);
     GB_CHECK_LAUNCH("embed_gather");

@@ -9,13 +9,14 @@ residual is fp32, and only the rows whose logits are wanted reach the final norm
 """
 from __future__ import annotations
 
+import inspect
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
 from .. import registry
 from ..cache import Cache
-from ..parts.base import Runtime
+from ..parts.base import RowStats, Runtime, fold_buffers, fold_weight
 from ..weights import InitScales, declare_model, load_tensors, random_tensors_on_device
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -51,6 +52,8 @@ class Model:
         self.embedding = tensors[spec.embedding.name]
         self.blocks = [registry.part_class("block", layer.block)(layer, layer.prefix, tensors, runtime)
                        for layer in spec.layers]
+        # a block arrangement may take the norm that follows it (to prepare the residual's rows for it)
+        self._takes_next_norm = ["next_norm" in inspect.signature(b.forward).parameters for b in self.blocks]
         norm_prefix = spec.final_norm_name[:-len("weight")]
         self.final_norm = registry.part_class("norm", spec.final_norm.kind)(spec.final_norm, norm_prefix, tensors, runtime)
         if spec.head.name in tensors:
@@ -133,10 +136,29 @@ class Model:
         ops = self.rt.ops
         rows = batch.rows
         h = torch.empty((rows, self.spec.hidden), dtype=torch.float32, device=self.rt.device)
-        ops.embed_gather(self.embedding, batch.ids, h)
-        delta = None
-        for pos, entry in enumerate(self.spec.schedule):
-            delta = self.blocks[entry.layer].forward(batch, h, delta, cache.view(pos))
+        # What is still owed to the residual travels from block to block: an addend not yet added, the
+        # rows' statistics (``RowStats``) where the last kernel left them, or nothing.
+        pending = None
+        schedule = self.spec.schedule
+        first = self.blocks[schedule[0].layer]
+        weight = None
+        if rows <= ops.STAT_ROWS and hasattr(first, "wants_stats") and first.wants_stats(rows):
+            weight = fold_weight(first.first_norm(), self.spec.hidden)
+        if weight is not None:
+            stats, prescaled = fold_buffers(batch, 0, self.spec.hidden)
+            ops.embed_gather(self.embedding, batch.ids, h, stats, weight, prescaled[:rows])
+            pending = RowStats(stats, 1, prescaled[:rows], first.first_norm())
+        else:
+            ops.embed_gather(self.embedding, batch.ids, h)
+        for pos, entry in enumerate(schedule):
+            block = self.blocks[entry.layer]
+            if self._takes_next_norm[entry.layer]:
+                after = self.blocks[schedule[pos + 1].layer] if pos + 1 < len(schedule) else None
+                next_norm = self.final_norm if after is None else (after.first_norm() if hasattr(after, "first_norm") else None)
+                pending = block.forward(batch, h, pending, cache.view(pos), next_norm=next_norm)
+            else:
+                pending = block.forward(batch, h, pending, cache.view(pos))
+        delta = pending if isinstance(pending, torch.Tensor) else None
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()

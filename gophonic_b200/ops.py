@@ -88,16 +88,40 @@ def _need(t: torch.Tensor, name: str, dtype=None, dim=None, contiguous=True) -> 
 
 
 # ---- embedding ---------------------------------------------------------------------------
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r, :] = float32(table[ids[r], :])."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stats: Optional[torch.Tensor] = None,
+                 next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = float32(table[ids[r], :]).  With ``stats`` (float32 [>= rows, capacity]) the sum of
+    squares of row r is left in stats[r, 0]: one partial sum a row.  With ``next_weight`` (float32
+    [hidden]) and ``next_x`` (bfloat16 [rows, hidden]) also next_x = bf16(out * next_weight): the
+    output of an RMSNorm with that weight but for each row's factor."""
     _need(table, "embed table", dim=2)
     _need(ids, "ids", torch.int32, 1)
     _need(out, "embed out", torch.float32, 2)
     rows, hidden = out.shape
     if ids.numel() != rows or table.shape[1] != hidden:
         raise KernelError(f"embed_gather: {ids.numel()} ids, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    stride = 0
+    if stats is not None:
+        _need(stats, "row statistics", torch.float32, 2)
+        if stats.shape[0] < rows:
+            raise KernelError(f"embed_gather: statistics for {stats.shape[0]} rows, {rows} rows")
+        stride = stats.stride(0)
+    ldxn = _check_next(next_weight, next_x, rows, hidden, "embed_gather")
     _check(_lib.gb_embed_gather(_ptr(table), _code(table.dtype), _ptr(ids), c_int(rows), c_int(hidden),
-                                c_int(table.shape[0]), _ptr(out), _stream()))
+                                c_int(table.shape[0]), _ptr(out), _ptr(stats), c_int64(stride), _ptr(next_weight), _ptr(next_x),
+                                c_int64(ldxn), _stream()))
+
+
+def _check_next(next_weight, next_x, rows: int, width: int, who: str) -> int:
+    if next_weight is None:
+        return 0
+    _need(next_weight, "next norm weight", torch.float32, 1)
+    if next_x is None:
+        raise KernelError(f"{who}: a norm weight is given without a tensor for the rows it scales")
+    _need(next_x, "prescaled rows", torch.bfloat16, 2, contiguous=False)
+    if next_weight.numel() != width or next_x.shape != (rows, width) or next_x.stride(1) != 1:
+        raise KernelError(f"{who}: norm weight of {next_weight.numel()}, prescaled rows {tuple(next_x.shape)} for {rows} x {width}")
+    return next_x.stride(0)
 
 
 # ---- cache pages, seeded fill ------------------------------------------------------------
@@ -238,6 +262,70 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
                                           c_int64(a.stride(0)), c_int64(out.stride(0)), _stream()))
     else:
         raise KernelError(f"gemm_swiglu: unknown algorithm '{algo}'")
+
+
+# ---- few-row products with the residual's row-wise work folded in ------------------------
+STAT_ROWS = 8   # rows a statistics buffer holds; the folded products take up to this many rows
+
+
+def _skinny_operands_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= STAT_ROWS
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.is_contiguous() and w.data_ptr() % 16 == 0)
+
+
+def gemm_scaled_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_scaled`` takes this product: up to 8 bfloat16 rows against bfloat16 weights
+    whose rows are 16-byte aligned, an output narrower than the head's."""
+    return _skinny_operands_ok(x, w) and w.shape[0] < WIDE_OUTPUT
+
+
+def gemm_scaled(x: torch.Tensor, eps: float, stats: torch.Tensor, stats_count: int, w: torch.Tensor, out: torch.Tensor,
+                swiglu: bool = False) -> None:
+    """out[r] = rs[r] * (x[r] @ w^T) with rs[r] = 1 / sqrt(sum_r / K + eps), sum_r the sum of the
+    ``stats_count`` partial sums stats[r, :stats_count]: the product of RMSNorm rows whose factor was
+    left out when ``x = bf16(h * norm_weight)`` was made (by ``gemm_residual`` or ``embed_gather``).
+    With ``swiglu``, ``w`` holds gate and up rows interleaved in blocks of eight and
+    out[M, N / 2] = silu(gate) * up."""
+    _need(x, "prescaled rows", torch.bfloat16, 2, contiguous=False)
+    _need(stats, "row statistics", torch.float32, 2)
+    _need(w, "gemm w", torch.bfloat16, 2)
+    _need(out, "gemm out", dim=2, contiguous=False)
+    M, K = x.shape
+    N = w.shape[0]
+    if (not gemm_scaled_accepts(x, w) or w.shape[1] != K or out.stride(1) != 1
+            or out.shape != (M, N // 2 if swiglu else N) or stats.shape[0] < M or not 0 < stats_count <= stats.shape[1]):
+        raise KernelError(f"gemm_scaled: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
+                          f"{stats_count} partial sums in {tuple(stats.shape)}")
+    _check(_lib.gb_gemm_skinny_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
+                                      c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
+                                      c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream()))
+
+
+def gemm_residual_accepts(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor) -> bool:
+    return _skinny_operands_ok(x, w) and h.dtype == torch.float32 and h.stride(1) == 1
+
+
+def gemm_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, stats: torch.Tensor,
+                  next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None) -> int:
+    """h += x @ w^T in place (``h`` float32: the residual stream; one float32 addition per element,
+    as a separate add gives) and stats[row, c] = the sum of squares of the 16 new values of the row
+    in columns 16 c .. 16 c + 15.  With ``next_weight`` also next_x = bf16(h * next_weight), the
+    rows ``gemm_scaled`` takes.  Returns the number of partial sums a row."""
+    _need(x, "gemm a", torch.bfloat16, 2, contiguous=False)
+    _need(w, "gemm w", torch.bfloat16, 2)
+    _need(h, "residual", torch.float32, 2, contiguous=False)
+    _need(stats, "row statistics", torch.float32, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    count = (N + 15) // 16
+    if not gemm_residual_accepts(x, w, h) or w.shape[1] != K or h.shape != (M, N) or stats.shape[0] < M or stats.shape[1] < count:
+        raise KernelError(f"gemm_residual: x {tuple(x.shape)}, w {tuple(w.shape)}, h {tuple(h.shape)}, statistics {tuple(stats.shape)}")
+    ldxn = _check_next(next_weight, next_x, M, N, "gemm_residual")
+    _check(_lib.gb_gemm_skinny_residual(_ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(h), c_int64(h.stride(0)), _ptr(stats),
+                                        c_int64(stats.stride(0)), _ptr(next_weight), _ptr(next_x), c_int64(ldxn),
+                                        c_int(M), c_int(N), c_int(K), _stream()))
+    return count
 
 
 # ---- matrix products ---------------------------------------------------------------------

@@ -16,7 +16,7 @@ from typing import List, Mapping, Optional
 import torch
 
 from .. import registry
-from .base import KVRequest, Mixer, Runtime, TensorDecl
+from .base import KVRequest, Mixer, RowStats, Runtime, TensorDecl, fold_weight, other_fold_buffers
 
 
 def choose_splits(units: int, max_kv_len: int, sm_count: int = 148, page_bytes: int = 32768) -> int:
@@ -125,16 +125,43 @@ class Attention(Mixer):
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
         self.rt.ops.gemm_add(self._context(batch, x, cache), self.o, h)
 
+    def folds_norm(self, rows: int, norm) -> bool:
+        """Single-token steps of up to eight rows in bfloat16: the q/k/v product applies the rows'
+        norm factors from the residual's statistics and the output projection adds into the residual."""
+        ops = self.rt.ops
+        return (rows <= ops.STAT_ROWS and self.rt.act_dtype == torch.bfloat16 and self.qkv.dtype == torch.bfloat16
+                and self.o.dtype == torch.bfloat16 and norm.rms_fold() is not None and self.spec.hidden % 8 == 0
+                and self.q_dim % 8 == 0 and self.qkv.shape[0] < ops.WIDE_OUTPUT and self.qkv.data_ptr() % 16 == 0
+                and self.o.data_ptr() % 16 == 0)
+
+    def forward_folded(self, batch, h: torch.Tensor, stats: RowStats, norm, cache, next_norm=None) -> RowStats:
+        ops = self.rt.ops
+        rows = h.shape[0]
+        _, eps = norm.rms_fold()
+        qkv = torch.empty((rows, self.q_dim + 2 * self.kv_dim), dtype=self.rt.act_dtype, device=h.device)
+        ops.gemm_scaled(stats.prescaled, eps, stats.partials, stats.count, self.qkv, qkv)
+        ctx = self._attend(batch, qkv, cache)
+        out_stats, out_rows = other_fold_buffers(batch, stats, self.spec.hidden)
+        weight = fold_weight(next_norm, self.spec.hidden)
+        count = ops.gemm_residual(ctx, self.o, h, out_stats, weight, out_rows[:rows] if weight is not None else None)
+        return RowStats(out_stats, count, out_rows[:rows] if weight is not None else None, next_norm if weight is not None else None)
+
     def _context(self, batch, x: torch.Tensor, cache) -> torch.Tensor:
         """Everything up to the output projection: [rows, heads * head_dim] in the activation dtype."""
-        ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
+        qkv = torch.empty((rows, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
+        self.rt.ops.gemm(x, self.qkv, qkv)
+        return self._attend(batch, qkv, cache)
+
+    def _attend(self, batch, qkv: torch.Tensor, cache) -> torch.Tensor:
+        """q/k norm, position encoding, cache write and attention on the rows of ``qkv``."""
+        ops, s = self.rt.ops, self.spec
+        rows = qkv.shape[0]
+        x = qkv
         if cache is None:
             raise ValueError("attention needs a key/value cache plane")
         if cache.k.dtype != x.dtype:
             raise ValueError(f"attention: cache holds {cache.k.dtype}, activations are {x.dtype}")
-        qkv = torch.empty((rows, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
-        ops.gemm(x, self.qkv, qkv)
         cos, sin, rot = self.position.kernel_args()
         ops.qk_norm_rope_kv_write(qkv, s.heads, s.kv_heads, s.head_dim, self.q_norm, self.k_norm, self.eps,
                                   cos, sin, rot, batch.row_pos, batch.row_seq, batch.seq_slot,

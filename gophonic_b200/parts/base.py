@@ -54,6 +54,49 @@ class StateRequest:
 
 
 @dataclass
+class RowStats:
+    """What travels between parts instead of a pending addend when the residual is already complete
+    and its statistics are known: ``partials[row, :count]`` are partial sums of squares of row
+    ``row`` of the residual, written by whichever kernel last changed it (a product that added its
+    output into the residual, or the embedding).  If that kernel was told which norm comes next,
+    ``prescaled`` holds bf16(residual * that norm's weight), the norm's output but for each row's
+    factor, and ``prescaled_for`` is that norm.  A part that can apply the factor in its own first
+    product (``folds_norm``) then needs no norm kernel; every other part ignores all this and
+    runs its norm as usual."""
+    partials: torch.Tensor                      # float32 [>= rows, capacity]
+    count: int
+    prescaled: Optional[torch.Tensor] = None    # bfloat16 [rows, width]
+    prescaled_for: Optional[object] = None
+
+
+def fold_buffers(batch, which: int, width: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One of the step's two pairs of buffers for ``RowStats`` (they alternate: a product reads one
+    pair while the next product that changes the residual writes the other): statistics, float32
+    [8, capacity] with room for one partial sum per 16 columns of a residual ``width`` wide, and
+    prescaled rows, bfloat16 [8, width]."""
+    capacity = max(8, (width + 15) // 16)
+    stats = batch.workspace(("row statistics", which & 1, capacity), 8 * capacity).view(8, capacity)
+    rows = batch.workspace(("prescaled rows", which & 1, width), 8 * width, torch.bfloat16).view(8, width)
+    return stats, rows
+
+
+def other_fold_buffers(batch, stats: RowStats, width: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The pair of buffers ``stats`` did not come in: nothing reads it any more."""
+    pair = fold_buffers(batch, 0, width)
+    if pair[0].data_ptr() == stats.partials.data_ptr():
+        pair = fold_buffers(batch, 1, width)
+    return pair
+
+
+def fold_weight(norm, width: int) -> Optional[torch.Tensor]:
+    """The weight of ``norm`` if a producing kernel can prescale rows of ``width`` for it, else None."""
+    fold = norm.rms_fold() if norm is not None and hasattr(norm, "rms_fold") else None
+    if fold is None or fold[0].numel() != width:
+        return None
+    return fold[0]
+
+
+@dataclass
 class Runtime:
     """What parts need to run: the device, the activation dtype of this model instance
     (torch.float32 for the true 32-bit path, torch.bfloat16 for the serving path) and the
@@ -84,6 +127,11 @@ class Norm(Part):
     in place); then out = norm(h) in the activation dtype.  With ``rows`` (int32 row indices) the
     sum h[rows] + delta[rows] is normalised into out[i] and h is left untouched."""
     category = "norm"
+
+    def rms_fold(self):
+        """(weight, eps) if this norm is y = x / sqrt(mean(x^2) + eps) * weight with a float32 weight
+        vector, so that a product's kernel may apply it from the residual's ``RowStats``; else None."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -117,6 +165,15 @@ class Mixer(Part):
         with.  Scratch memory that the plan calls for comes from ``batch.workspace(key, n)``."""
         return None
 
+    def folds_norm(self, rows: int, norm) -> bool:
+        """True if, for a step of ``rows`` rows, ``forward_folded(batch, h, stats, norm, cache,
+        next_norm)`` can run: the part then takes its activations from ``stats.prescaled`` (made for
+        ``norm``), applies the rows' factors from the statistics in its first product, adds its
+        output into the float32 residual ``h`` in its last product and returns the new ``RowStats``,
+        prescaled for ``next_norm`` if that is given and can be.  Only offered where it is faster
+        (single-token steps of a few rows); the default is False."""
+        return False
+
     def adds_in_place(self, rows: int) -> bool:
         """True if, for a step of ``rows`` rows, ``forward_into(batch, x, h, cache)`` is the faster
         way: the part then adds its output to the fp32 residual ``h`` itself (in the epilogue of its
@@ -129,6 +186,10 @@ class FeedForward(Part):
     """forward(batch, x, out): x [rows, hidden] activation dtype -> out [rows, hidden] fp32.
     Optionally ``adds_in_place(rows)`` / ``forward_into(batch, x, h)`` as for a mixer."""
     category = "feed_forward"
+
+    def folds_norm(self, rows: int, norm) -> bool:
+        """As for a mixer: ``forward_folded(batch, h, stats, norm, next_norm) -> RowStats``."""
+        return False
 
     def adds_in_place(self, rows: int) -> bool:
         return False

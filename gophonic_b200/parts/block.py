@@ -2,11 +2,16 @@
 
 ``PreNormBlock``: h += mixer(norm_m(h)); h += ffn(norm_f(h)).  A part's output is either added to
 the residual by the part itself, in the epilogue of its last product (prompt-sized steps of the
-built-in parts: ``adds_in_place``), or it is not added at once: it is handed on as ``delta`` and
-added by whatever norms the residual next (the layer's second norm, the next block's first norm,
-or the final norm), in the same kernel that takes the statistics
-(internal/qwen3lm/evaluator.go:641-647, 678-682; ops.go:94-108 does the same).  The residual h
-stays fp32 throughout.
+built-in parts: ``adds_in_place``), or it is not added at once: it is handed on as a pending
+addend and added by whatever norms the residual next (the layer's second norm, the next block's
+first norm, or the final norm), in the same kernel that takes the statistics
+(internal/qwen3lm/evaluator.go:641-647, 678-682; ops.go:94-108 does the same).  In single-token
+steps of a few rows the built-in parts go one step further (``folds_norm``): the part's last
+product adds into the residual, leaves the rows' sums of squares behind and writes the rows
+already multiplied by the next norm's weight (``RowStats``), and the next part's first product
+multiplies its finished sums by the rows' factors, so no norm kernel runs at all
+(internal/qwen3lm/gpu.metal:70-162 folds its norms in the same spirit).  The residual h stays
+fp32 throughout.
 """
 from __future__ import annotations
 
@@ -15,7 +20,7 @@ from typing import List, Mapping, Optional
 import torch
 
 from .. import registry
-from .base import Part, Runtime, TensorDecl
+from .base import Part, RowStats, Runtime, TensorDecl
 
 
 class PreNormBlock(Part):
@@ -65,20 +70,43 @@ class PreNormBlock(Part):
     def capturable(self) -> bool:
         return all(p.capturable for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward))
 
-    def forward(self, batch, h: torch.Tensor, delta: Optional[torch.Tensor], cache) -> torch.Tensor:
-        """Runs the layer on residual ``h`` (fp32, updated in place) with the pending addend
-        ``delta`` (or None); returns the new pending addend (None if everything is added)."""
+    def first_norm(self):
+        """The norm that reads the residual first: whoever changes the residual ahead of this block
+        may prepare its rows for it."""
+        return self.mixer_norm
+
+    def wants_stats(self, rows: int) -> bool:
+        """Whether the block's first part would apply its norm's row factors itself if the residual
+        came with ``RowStats`` prescaled for ``first_norm()``."""
+        return self.mixer.folds_norm(rows, self.mixer_norm)
+
+    def forward(self, batch, h: torch.Tensor, pending, cache, next_norm=None):
+        """Runs the layer on residual ``h`` (fp32, updated in place).  ``pending`` says what is still
+        owed to the residual: a float32 tensor that has yet to be added, ``RowStats`` (nothing owed,
+        the rows' sums of squares are known and the rows may be prescaled for a norm), or None
+        (nothing owed, nothing known).  ``next_norm`` is the norm that will read the residual after
+        this layer, if the caller knows it.  Returns what is owed for the layer after."""
         rows, hidden = h.shape
         act = self.rt.act_dtype
-        x = torch.empty((rows, hidden), dtype=act, device=h.device)
-        self.mixer_norm.forward(h, x, delta)
-        if self.mixer.adds_in_place(rows):
-            self.mixer.forward_into(batch, x, h, cache)   # h += mixer(x) in the mixer's own last kernel
-            mixed = None
+        x = None
+        if (isinstance(pending, RowStats) and pending.prescaled_for is self.mixer_norm
+                and self.mixer.folds_norm(rows, self.mixer_norm)):
+            pending = self.mixer.forward_folded(batch, h, pending, self.mixer_norm, cache, self.feed_forward_norm)
         else:
-            mixed = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
-            self.mixer.forward(batch, x, mixed, cache)
-        self.feed_forward_norm.forward(h, x, mixed)
+            x = torch.empty((rows, hidden), dtype=act, device=h.device)
+            self.mixer_norm.forward(h, x, pending if isinstance(pending, torch.Tensor) else None)
+            if self.mixer.adds_in_place(rows):
+                self.mixer.forward_into(batch, x, h, cache)   # h += mixer(x) in the mixer's own last kernel
+                pending = None
+            else:
+                pending = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
+                self.mixer.forward(batch, x, pending, cache)
+        if (isinstance(pending, RowStats) and pending.prescaled_for is self.feed_forward_norm
+                and self.feed_forward.folds_norm(rows, self.feed_forward_norm)):
+            return self.feed_forward.forward_folded(batch, h, pending, self.feed_forward_norm, next_norm)
+        if x is None:
+            x = torch.empty((rows, hidden), dtype=act, device=h.device)
+        self.feed_forward_norm.forward(h, x, pending if isinstance(pending, torch.Tensor) else None)
         if self.feed_forward.adds_in_place(rows):
             self.feed_forward.forward_into(batch, x, h)
             return None

@@ -23,6 +23,9 @@ class RMSNorm(Norm):
         self.weight = tensors[prefix + "weight"].to(torch.float32).contiguous()
         self.eps = float(spec.eps)
 
+    def rms_fold(self):
+        return self.weight, self.eps
+
     def forward(self, h: torch.Tensor, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None) -> None:
         self.rt.ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)

@@ -7,7 +7,7 @@ from typing import List, Mapping
 
 import torch
 
-from .base import FeedForward, Runtime, TensorDecl
+from .base import FeedForward, RowStats, Runtime, TensorDecl, fold_weight, other_fold_buffers
 
 
 class SwiGLU(FeedForward):
@@ -50,6 +50,26 @@ class SwiGLU(FeedForward):
 
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor) -> None:
         self.rt.ops.gemm_add(self._activation(x), self.down, h)
+
+    def folds_norm(self, rows: int, norm) -> bool:
+        """Single-token steps of up to eight rows in bfloat16, gate and up interleaved: the gate/up
+        product applies the rows' norm factors from the residual's statistics, the down projection
+        adds into the residual."""
+        ops = self.rt.ops
+        return (rows <= ops.STAT_ROWS and self.interleaved and self.rt.act_dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16
+                and norm.rms_fold() is not None and self.spec.hidden % 8 == 0 and self.spec.intermediate % 8 == 0
+                and self.gate_up.shape[0] < ops.WIDE_OUTPUT and self.gate_up.data_ptr() % 16 == 0 and self.down.data_ptr() % 16 == 0)
+
+    def forward_folded(self, batch, h: torch.Tensor, stats: RowStats, norm, next_norm=None) -> RowStats:
+        ops = self.rt.ops
+        rows = h.shape[0]
+        _, eps = norm.rms_fold()
+        act = torch.empty((rows, self.spec.intermediate), dtype=self.rt.act_dtype, device=h.device)
+        ops.gemm_scaled(stats.prescaled, eps, stats.partials, stats.count, self.gate_up, act, swiglu=True)
+        out_stats, out_rows = other_fold_buffers(batch, stats, self.spec.hidden)
+        weight = fold_weight(next_norm, self.spec.hidden)
+        count = ops.gemm_residual(act, self.down, h, out_stats, weight, out_rows[:rows] if weight is not None else None)
+        return RowStats(out_stats, count, out_rows[:rows] if weight is not None else None, next_norm if weight is not None else None)
 
     def _activation(self, x: torch.Tensor) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T): [rows, intermediate] in the activation dtype."""

@@ -114,6 +114,102 @@ def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
     close(out2, ref, 1.2e-2)
 
 
+# ---- few-row products with the norm and the residual add folded in ---------------------------
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K,count", [(64, 64, 1), (1000, 96, 5), (6144, 4096, 256), (136, 2048, 128), (40, 520, 33)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_that_applies_the_rows_norm_factors_from_statistics(ops, M, N, K, count, out_dtype):
+    """out = rmsnorm(h) w^T where the rows arrive as bf16(h * norm weight) and each row's sum of
+    squares as ``count`` partial sums (here: of uneven column blocks): the kernel adds them up and
+    multiplies its finished sums by 1 / sqrt(mean + eps)."""
+    eps = 2e-6
+    h, nw = rnd(M, K, scale=3.0, seed=1), 1 + 0.1 * rnd(K, seed=2)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=3)
+    edges = torch.linspace(0, K, count + 1).round().long().tolist()
+    stats = torch.full((8, max(count, 8) + 3), float("nan"), device=DEV)
+    for c in range(count):
+        stats[:M, c] = (h[:, edges[c]:edges[c + 1]].double() ** 2).sum(-1).float()
+    x = (h * nw).to(torch.bfloat16)
+    rs = 1.0 / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
+    ref = rs * (x.double() @ w.double().T)
+    assert ops.gemm_scaled_accepts(x, w)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_scaled(x, eps, stats, count, w, out)
+    close(out, ref, 2e-5 if out_dtype == torch.float32 else 6e-3)
+    # against the norm itself: the rows were rounded to bfloat16 before instead of after the factor
+    exact = (h.double() * rs * nw.double()) @ w.double().T
+    close(out, exact, 1.2e-2)
+    if M > 1:   # a row's result does not depend on the other rows
+        one = torch.empty((1, N), dtype=out_dtype, device=DEV)
+        ops.gemm_scaled(x[M - 1:].contiguous(), eps, stats[M - 1:].contiguous(), count, w, one)
+        assert torch.equal(one[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (12288 // 8, 512)])
+def test_gemm_that_applies_the_rows_norm_factors_with_the_swiglu_epilogue(ops, M, inter, K):
+    eps = 1e-6
+    gate, up = rnd(inter, K, dtype=torch.bfloat16, scale=0.2, seed=1), rnd(inter, K, dtype=torch.bfloat16, scale=0.2, seed=2)
+    w = torch.stack([gate.view(inter // 8, 8, K), up.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
+    h, nw = rnd(M, K, scale=2.0, seed=3), 1 + 0.1 * rnd(K, seed=4)
+    stats = torch.zeros((8, 8), device=DEV)
+    stats[:M, 0] = (h.double() ** 2).sum(-1).float()
+    x = (h * nw).to(torch.bfloat16)
+    rs = 1.0 / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
+    g, u = rs * (x.double() @ gate.double().T), rs * (x.double() @ up.double().T)
+    out = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_scaled(x, eps, stats, 1, w, out, swiglu=True)
+    close(out, g / (1 + torch.exp(-g)) * u, 6e-3)
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+@pytest.mark.parametrize("N,K", [(64, 64), (1000, 96), (4096, 12288), (4096, 4096), (40, 520)])
+def test_gemm_that_adds_into_the_residual_and_prepares_the_next_norm(ops, M, N, K):
+    """h += x w^T in the product's own epilogue: the bits of the product into a buffer and a float32
+    add; one partial sum of squares of the new residual per 16 columns; and the new rows times the
+    next norm's weight, rounded to bfloat16."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+    h0, nw = rnd(M, N, seed=3), 1 + 0.1 * rnd(N, seed=4)
+    prod = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ops.gemm(x, w, prod, algo="skinny")
+    h = h0.clone()
+    count = (N + 15) // 16
+    stats = torch.full((8, count + 2), float("nan"), device=DEV)
+    nxt = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.gemm_residual_accepts(x, w, h)
+    assert ops.gemm_residual(x, w, h, stats, nw, nxt) == count
+    assert torch.equal(h, h0 + prod)
+    close(h, h0.double() + x.double() @ w.double().T, 2e-5)
+    assert torch.equal(nxt, (h * nw).to(torch.bfloat16))
+    pad = torch.zeros((M, count * 16), dtype=torch.float64, device=DEV)
+    pad[:, :N] = h.double()
+    want = (pad ** 2).view(M, count, 16).sum(-1)
+    assert (stats[:M, :count].double() - want).abs().max() <= 1e-5 * want.abs().max()
+    assert torch.isnan(stats[M:]).all() and torch.isnan(stats[:, count:]).all()      # nothing else is written
+    # without a next norm only the residual and the statistics are written
+    h2, stats2 = h0.clone(), torch.zeros((8, count), device=DEV)
+    ops.gemm_residual(x, w, h2, stats2)
+    assert torch.equal(h2, h) and torch.equal(stats2[:M], stats[:M, :count])
+    with pytest.raises(ops.KernelError):
+        ops.gemm_residual(rnd(9, K, dtype=torch.bfloat16), w, torch.zeros((9, N), device=DEV), torch.zeros((9, count), device=DEV))
+    with pytest.raises(ops.KernelError, match="without a tensor"):
+        ops.gemm_residual(x, w, h2, stats2, nw, None)
+
+
+def test_embedding_leaves_row_statistics_and_prepares_the_first_norm(ops):
+    table = rnd(333, 72, dtype=torch.bfloat16)
+    ids = torch.tensor([0, 332, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty((5, 72), dtype=torch.float32, device=DEV)
+    stats = torch.full((8, 9), float("nan"), device=DEV)
+    nw = 1 + 0.1 * rnd(72, seed=4)
+    nxt = torch.empty((5, 72), dtype=torch.bfloat16, device=DEV)
+    ops.embed_gather(table, ids, out, stats, nw, nxt)
+    assert torch.equal(out, table[ids.long()].float())
+    assert torch.equal(nxt, (out * nw).to(torch.bfloat16))
+    want = (out.double() ** 2).sum(-1)
+    assert (stats[:5, 0].double() - want).abs().max() <= 1e-6 * want.max() and torch.isnan(stats[:, 1:]).all()
+
+
 # ---- matrix products ----------------------------------------------------------------------
 SHAPES = [(1, 64, 64), (3, 1000, 96), (17, 136, 80), (64, 333, 160), (65, 192, 96), (130, 520, 264), (257, 96, 4104)]
 
