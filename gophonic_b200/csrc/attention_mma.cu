@@ -14,29 +14,10 @@
 // Scores, the softmax and the output accumulators are fp32; probabilities are rounded to
 // bfloat16 for the second product, as the values are bfloat16.
 #include "mma.cuh"
+#include "api.h"
 
 #include <math.h>
 
-struct AttnParams {
-    const void* q;
-    int64_t q_row_stride;
-    void* out;
-    int64_t out_row_stride;
-    const void* k_plane;
-    const void* v_plane;
-    const int* block_table;
-    int bt_stride;
-    const int* seq_slot;
-    const int* seq_q_start;
-    const int* seq_q_len;
-    const int* seq_kv_len;
-    int nseq, heads, kv_heads, d;
-    int max_q_len;
-    float scale;
-    int window;
-    int num_splits;
-    float* scratch;
-};
 
 int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
                               int nseq, int heads, int d, int num_splits, cudaStream_t stream);

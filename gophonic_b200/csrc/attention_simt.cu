@@ -9,29 +9,10 @@
 // (internal/qwen3lm/ops.go:259-293): a row's result does not depend on how its sequence was cut
 // into steps or on what else is in the batch.
 #include "common.cuh"
+#include "api.h"
 
 #include <math.h>
 
-struct AttnParams {
-    const void* q;
-    int64_t q_row_stride;
-    void* out;
-    int64_t out_row_stride;
-    const void* k_plane;
-    const void* v_plane;
-    const int* block_table;
-    int bt_stride;
-    const int* seq_slot;
-    const int* seq_q_start;
-    const int* seq_q_len;
-    const int* seq_kv_len;
-    int nseq, heads, kv_heads, d;
-    int max_q_len;
-    float scale;
-    int window;
-    int num_splits;
-    float* scratch;  // [nseq][heads][num_splits][d + 2] when num_splits > 1
-};
 
 namespace {
 

@@ -21,29 +21,10 @@
 // continues a cached prefix needs nothing special.  All barrier waits are bounded; a wait that
 // gives up sets a status word (gb_attention_tc5_status) and the CTA runs out.
 #include "tc5.cuh"
+#include "api.h"
 
 #include <math.h>
 
-struct AttnParams {
-    const void* q;
-    int64_t q_row_stride;
-    void* out;
-    int64_t out_row_stride;
-    const void* k_plane;
-    const void* v_plane;
-    const int* block_table;
-    int bt_stride;
-    const int* seq_slot;
-    const int* seq_q_start;
-    const int* seq_q_len;
-    const int* seq_kv_len;
-    int nseq, heads, kv_heads, d;
-    int max_q_len;
-    float scale;
-    int window;
-    int num_splits;
-    float* scratch;
-};
 
 namespace {
 

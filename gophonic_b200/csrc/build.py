@@ -41,8 +41,9 @@ SOURCES = [
     "attention_tc5.cu",
     "sampling.cu",
     "no_alloc.cu",
+    "dispatch.cu",
 ]
-HEADERS = ["common.cuh", "mma.cuh", "tc5.cuh", "no_alloc.h"]
+HEADERS = ["common.cuh", "mma.cuh", "tc5.cuh", "no_alloc.h", "api.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

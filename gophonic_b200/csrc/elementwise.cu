@@ -1,6 +1,7 @@
 // Row-wise kernels: embedding gather, residual add + RMSNorm, SwiGLU, and the fused
 // per-head norm + rotary embedding + cache write.  All arithmetic is fp32; only storage varies.
 #include "common.cuh"
+#include "api.h"
 
 #include <stdarg.h>
 #include <stdio.h>
@@ -322,26 +323,6 @@ GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, 
 //   v heads: stored as they are in the value plane.
 // One warp per (row, head).  The angle table holds cos/sin of pos * theta^(-2i/rot) computed in
 // float64 on the host and rounded to fp32 (internal/qwen3lm/evaluator.go:847-858).
-struct QkRopeParams {
-    void* qkv;
-    int64_t row_stride;
-    const float* q_w;
-    const float* k_w;
-    float eps;
-    const float* cos_t;  // [capacity, rot/2] or null when rot == 0
-    const float* sin_t;
-    int rot;             // rotary width (even, <= d); 0: no rotation
-    int table_positions;
-    const int* row_pos;
-    const int* row_seq;
-    const int* seq_slot;
-    const int* block_table;
-    int bt_stride;
-    void* k_plane;
-    void* v_plane;
-    int write_kv;
-    int rows, heads, kv_heads, d;
-};
 
 template <typename T>
 __global__ void qk_rope_kernel(QkRopeParams p) {

@@ -1,29 +1,10 @@
 // See no_alloc.h: single-token split-key attention whose scratch is a static device array.
 #include "no_alloc.h"
+#include "api.h"
 
 #include "common.cuh"
 
 // the layout of attention_simt.cu's parameters
-struct AttnParams {
-    const void* q;
-    int64_t q_row_stride;
-    void* out;
-    int64_t out_row_stride;
-    const void* k_plane;
-    const void* v_plane;
-    const int* block_table;
-    int bt_stride;
-    const int* seq_slot;
-    const int* seq_q_start;
-    const int* seq_q_len;
-    const int* seq_kv_len;
-    int nseq, heads, kv_heads, d;
-    int max_q_len;
-    float scale;
-    int window;
-    int num_splits;
-    float* scratch;
-};
 
 extern "C" int gb_attention_simt(const AttnParams* pp, int dtype, cudaStream_t stream);
 

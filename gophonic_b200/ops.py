@@ -390,34 +390,23 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     return algo
 
 
+_ALGO_NAMES = ("simt", "skinny", "tc5", "tc5_pair", "tc5_decode")
+
+
 def gemm_algo(M: int, N: int, K: int) -> str:
-    """The tensor-core kernel ``gemm`` picks for aligned bfloat16 operands of these sizes (measured
-    on the four products of an 8B layer, 1 to 2048 rows)."""
-    if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT:
-        return "skinny"            # weights streamed straight into mma.sync fragments
-    if M <= 64:
-        return "tc5_decode"        # tcgen05, weights on the M side, K slices across a cluster
-    if M <= TC5_DECODE_MAX_ROWS // 2:
-        # up to 128 rows the step is still bound by reading the weights: the decode kernel gives
-        # every SM a share of them, the tiled kernel only where the output is wide enough for that
-        return "tc5_decode" if (N + 127) // 128 < _sms() else "tc5"
-    if M <= TC5_DECODE_MAX_ROWS and (N + 255) // 256 <= 16 and K >= 8192:
-        return "tc5_decode"        # a narrow output with a long K: too few tiles for the tiled kernels
-    if M >= TC5_PAIR_MIN_ROWS:
-        return "tc5_pair"          # tcgen05 on pairs of SMs, 256 x 256 tiles
-    return "tc5"                   # tcgen05, 128 x 256 tiles
+    """The tensor-core kernel ``gemm`` picks for aligned bfloat16 operands of these sizes: up to 8 rows
+    the fragment-streaming kernel, up to 128 (256 for narrow outputs with a long K) the tcgen05
+    decode kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs two SMs
+    on a tile.  The rule lives in the library (``gb_gemm_algo``), which also applies it when it
+    issues a whole layer itself."""
+    return _ALGO_NAMES[int(_lib.gb_gemm_algo(c_int(M), c_int(N), c_int(K), c_int(_sms())))]
 
 
-# rows up to which the tcgen05 decode kernel takes a product (its batch side is one instruction wide)
-TC5_DECODE_MAX_ROWS = 256
-# rows from which the tcgen05 kernel that pairs two SMs on tiles of 256 x 256 is used
-TC5_PAIR_MIN_ROWS = 192
-# rows up to which the fragment-streaming kernel is used for decode; above it (to 64) the tcgen05
-# split-K kernel takes over
-SKINNY_MAX_ROWS = 8
-# outputs this wide (the head) have enough tiles to fill the GPU without cutting K; the tcgen05
-# kernel then streams them a little faster than the fragment kernel at every row count
-WIDE_OUTPUT = 32768
+# the rule's thresholds, as the library holds them: rows up to which the fragment-streaming kernel
+# is used, rows up to which the tcgen05 decode kernel takes a product, rows from which two SMs are
+# paired on a tile, and the output width from which the decode kernel takes every row count
+SKINNY_MAX_ROWS, TC5_DECODE_MAX_ROWS, TC5_PAIR_MIN_ROWS, WIDE_OUTPUT, TC5_ATTENTION_MIN_ROWS = (
+    int(_lib.gb_dispatch_constant(c_int(i))) for i in range(5))
 
 _sm_count = {}
 
@@ -514,11 +503,6 @@ class _AttnParams(Structure):
     ]
 
 
-# prompts whose longest sequence brings at least this many rows use the tcgen05 attention kernel
-# (tiles of 128 query rows); shorter ones the mma.sync kernel (tiles of 64)
-TC5_ATTENTION_MIN_ROWS = 65
-
-
 def attention_scratch_floats(nseq: int, heads: int, head_dim: int, num_splits: int) -> int:
     return nseq * heads * num_splits * (head_dim + 2)
 
@@ -554,16 +538,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
                     block_table.data_ptr(), block_table.stride(0), seq_slot.data_ptr(),
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr())
-    if algo == "auto":
-        algo = "simt"
-        if q.dtype == torch.bfloat16 and head_dim % 16 == 0 and (head_dim <= 128 or head_dim == 256):
-            if max_q_len == 1:
-                algo = "decode_mma"
-            elif (max_q_len >= TC5_ATTENTION_MIN_ROWS and head_dim == 128
-                  and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0):
-                algo = "prefill_tc5"
-            else:
-                algo = "prefill_mma"
+    if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
+        algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
     if algo == "simt":
         _check(_lib.gb_attention_simt(byref(p), _code(q.dtype), _stream()), nk)
@@ -576,6 +552,69 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
     else:
         raise KernelError(f"attention: unknown algorithm '{algo}'")
     return algo
+
+
+# ---- a whole pre-norm layer from one call ---------------------------------------------------
+class PrenormLayer(Structure):
+    """Sizes, constants and tensors of one pre-norm layer of attention and SwiGLU (``GbPrenormLayer``)."""
+    _fields_ = [
+        ("hidden", c_int), ("heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("intermediate", c_int),
+        ("mixer_norm_eps", c_float), ("ffn_norm_eps", c_float), ("qk_norm_eps", c_float), ("scale", c_float),
+        ("window", c_int), ("rotary_dim", c_int), ("table_positions", c_int), ("act_dtype", c_int), ("gate_up_interleaved", c_int),
+        ("mixer_norm_w", c_void_p), ("ffn_norm_w", c_void_p), ("w_qkv", c_void_p), ("w_qkv_dtype", c_int), ("w_o", c_void_p),
+        ("w_o_dtype", c_int), ("w_gate_up", c_void_p), ("w_gate_up_dtype", c_int), ("w_down", c_void_p), ("w_down_dtype", c_int),
+        ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("cos_t", c_void_p), ("sin_t", c_void_p),
+    ]
+
+
+class _StepRows(Structure):
+    _fields_ = [
+        ("rows", c_int), ("nseq", c_int), ("max_q_len", c_int), ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p),
+        ("seq_q_start", c_void_p), ("seq_q_len", c_void_p), ("seq_kv_len", c_void_p), ("num_splits", c_int), ("split_scratch", c_void_p),
+        ("block_table", c_void_p), ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p), ("pages", c_int), ("write_kv", c_int),
+    ]
+
+
+_lib.gb_prenorm_layer_workspace.restype = c_int64
+
+
+def prenorm_layer_workspace(layer: PrenormLayer, rows: int) -> int:
+    """Bytes of workspace ``prenorm_layer_forward`` needs for a step of ``rows`` rows."""
+    return int(_lib.gb_prenorm_layer_workspace(byref(layer), c_int(rows)))
+
+
+def prenorm_layer_forward(layer: PrenormLayer, batch, cache, h: torch.Tensor, delta: Optional[torch.Tensor],
+                          workspace: torch.Tensor, num_splits: int = 1, split_scratch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Issue every kernel of one pre-norm layer (norm, q/k/v product, q/k norm + rotation + cache
+    write, attention, output projection, norm, gate/up product with SwiGLU, down projection) from one
+    call into the library: the kernels, their order and their choice by size are those of the
+    part-by-part path.  ``h`` is the float32 residual, updated in place; ``delta`` an addend it is
+    still owed (added by the first norm).  Returns the addend the layer leaves owed (a view into
+    ``workspace``), or None if its products added into the residual themselves."""
+    _need(h, "residual", torch.float32, 2)
+    _need(workspace, "layer workspace", torch.uint8, 1)
+    rows = h.shape[0]
+    if h.shape[1] != layer.hidden or rows != batch.rows:
+        raise KernelError(f"prenorm_layer: residual {tuple(h.shape)} for {batch.rows} rows of {layer.hidden}")
+    if delta is not None:
+        _need(delta, "delta", torch.float32, 2)
+        if delta.shape != h.shape:
+            raise KernelError(f"prenorm_layer: delta {tuple(delta.shape)} vs residual {tuple(h.shape)}")
+    if cache.k.dtype != (torch.bfloat16 if layer.act_dtype == BF16 else torch.float32):
+        raise KernelError(f"prenorm_layer: the cache holds {cache.k.dtype}")
+    step = _StepRows(rows, batch.nseq, batch.max_q_len, batch.row_pos.data_ptr(), batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(),
+                     batch.seq_q_start.data_ptr(), batch.seq_q_len.data_ptr(), batch.seq_kv_len.data_ptr(), num_splits,
+                     0 if split_scratch is None else split_scratch.data_ptr(), cache.block_table.data_ptr(), cache.block_table.stride(0),
+                     cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], 1 if cache.writable else 0)
+    out_ptr, n = c_void_p(0), c_int(0)
+    _check(_lib.gb_prenorm_layer_forward(byref(layer), byref(step), _ptr(h), _ptr(delta), _ptr(workspace), c_int64(workspace.numel()),
+                                         c_int(_sms()), byref(out_ptr), byref(n), _stream()), 0)
+    global launches
+    launches += n.value
+    if not out_ptr.value:
+        return None
+    at = out_ptr.value - workspace.data_ptr()
+    return workspace[at:at + 4 * rows * layer.hidden].view(torch.float32).view(rows, layer.hidden)
 
 
 # ---- sampling ----------------------------------------------------------------------------

@@ -146,6 +146,15 @@ class Attention(Mixer):
         count = ops.gemm_residual(ctx, self.o, h, out_stats, weight, out_rows[:rows] if weight is not None else None)
         return RowStats(out_stats, count, out_rows[:rows] if weight is not None else None, next_norm if weight is not None else None)
 
+    def key_splits(self, batch):
+        """(pieces the keys are cut into for this step, scratch for their partial results or None)."""
+        s = self.spec
+        splits = int(batch.plan_for(self) or 1)
+        if splits <= 1:
+            return 1, None
+        return splits, batch.workspace(("attention key splits", s.heads, s.head_dim, splits),
+                                       self.rt.ops.attention_scratch_floats(batch.nseq, s.heads, s.head_dim, splits))
+
     def _context(self, batch, x: torch.Tensor, cache) -> torch.Tensor:
         """Everything up to the output projection: [rows, heads * head_dim] in the activation dtype."""
         rows = x.shape[0]
@@ -167,10 +176,7 @@ class Attention(Mixer):
                                   cos, sin, rot, batch.row_pos, batch.row_seq, batch.seq_slot,
                                   cache.block_table, cache.k, cache.v, cache.writable)
         ctx = torch.empty((rows, self.q_dim), dtype=x.dtype, device=x.device)
-        splits, scratch = int(batch.plan_for(self) or 1), None
-        if splits > 1:   # partial results of the pieces, merged by a second kernel
-            scratch = batch.workspace(("attention key splits", s.heads, s.head_dim, splits),
-                                      ops.attention_scratch_floats(batch.nseq, s.heads, s.head_dim, splits))
+        splits, scratch = self.key_splits(batch)
         ops.attention(qkv[:, :self.q_dim], ctx, cache.k, cache.v, cache.block_table,
                       batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len, batch.nseq,
                       batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),

@@ -50,6 +50,37 @@ class PreNormBlock(Part):
             layer.feed_forward_norm, p + layer.feed_forward_norm_prefix, tensors, runtime)
         self.feed_forward = registry.part_class("feed_forward", layer.feed_forward.kind)(
             layer.feed_forward, p + layer.feed_forward_prefix, tensors, runtime)
+        self._native = None       # the library's record of this layer, if it can issue the layer itself
+        self._native_tables = None
+
+    def _native_layer(self):
+        """The layer as the library's one-call issue takes it, if mixer, feed-forward and norms are
+        exactly the built-in attention, SwiGLU and RMSNorm (a subclass may have changed what they
+        compute); None otherwise."""
+        from .attention import Attention
+        from .norm import RMSNorm
+        from .rope import NoPosition, RotaryEmbedding
+        from .swiglu import SwiGLU
+        m, f = self.mixer, self.feed_forward
+        if not (type(m) is Attention and type(f) is SwiGLU and type(self.mixer_norm) is RMSNorm
+                and type(self.feed_forward_norm) is RMSNorm and type(m.position) in (RotaryEmbedding, NoPosition)):
+            return None
+        ops = self.rt.ops
+        cos, sin, rot = m.position.kernel_args()
+        tables = (None if cos is None else cos.data_ptr(), None if sin is None else sin.data_ptr())
+        if self._native is not None and tables == self._native_tables:
+            return self._native
+        code = {torch.float32: ops.F32, torch.bfloat16: ops.BF16}
+        ptr = lambda t: 0 if t is None else t.data_ptr()
+        s = m.spec
+        self._native = ops.PrenormLayer(
+            s.hidden, s.heads, s.kv_heads, s.head_dim, f.spec.intermediate, self.mixer_norm.eps, self.feed_forward_norm.eps,
+            m.eps, float(s.scale), int(s.window), rot, 0 if cos is None else cos.shape[0], code[self.rt.act_dtype],
+            1 if f.interleaved else 0, ptr(self.mixer_norm.weight), ptr(self.feed_forward_norm.weight),
+            ptr(m.qkv), code[m.qkv.dtype], ptr(m.o), code[m.o.dtype], ptr(f.gate_up), code[f.gate_up.dtype],
+            ptr(f.down), code[f.down.dtype], ptr(m.q_norm), ptr(m.k_norm), ptr(cos), ptr(sin))
+        self._native_tables = tables
+        return self._native
 
     # What a model asks of a block, whatever its arrangement: the cache its runs need, tables for a
     # capacity, its mixers' launch plans, the weight bytes of one run, and whether it can be captured.
@@ -89,8 +120,18 @@ class PreNormBlock(Part):
         rows, hidden = h.shape
         act = self.rt.act_dtype
         x = None
-        if (isinstance(pending, RowStats) and pending.prescaled_for is self.mixer_norm
-                and self.mixer.folds_norm(rows, self.mixer_norm)):
+        folds = (isinstance(pending, RowStats) and pending.prescaled_for is self.mixer_norm
+                 and self.mixer.folds_norm(rows, self.mixer_norm))
+        native = None if folds or cache is None else self._native_layer()
+        if native is not None:
+            # the whole layer from one call into the library: the same kernels in the same order
+            ops = self.rt.ops
+            work = batch.workspace(("prenorm layer", ops.prenorm_layer_workspace(native, rows)),
+                                   ops.prenorm_layer_workspace(native, rows), torch.uint8)
+            splits, scratch = self.mixer.key_splits(batch)
+            return ops.prenorm_layer_forward(native, batch, cache, h, pending if isinstance(pending, torch.Tensor) else None,
+                                             work, splits, scratch)
+        if folds:
             pending = self.mixer.forward_folded(batch, h, pending, self.mixer_norm, cache, self.feed_forward_norm)
         else:
             x = torch.empty((rows, hidden), dtype=act, device=h.device)

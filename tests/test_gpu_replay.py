@@ -423,6 +423,41 @@ def test_a_batch_that_shrinks_is_replayed_at_a_few_captured_sizes(model_dirs, re
     assert eng.cache.pages.held() == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_a_layer_issued_by_the_library_equals_the_layer_issued_part_by_part(model_dirs, plain_models, name, dtype):
+    """The built-in layer is issued from one call into the library (the same kernels, chosen by the
+    same rule, out of one workspace); with that switched off the parts issue their kernels one by
+    one.  Both give the same bits: prompts of every size class in one step, steps of 20 single
+    tokens, and single tokens of a few sequences."""
+    from gophonic_b200.engine import Engine, Model
+    cfg, _ = plain_models[name]
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in (300, 65, 9, 1, 130, 200)] + \
+              [rng.integers(0, cfg["vocab_size"], size=3).tolist() for _ in range(14)]
+    follow = rng.integers(0, cfg["vocab_size"], size=(4, len(prompts)))
+    outs = []
+    for native in (True, False):
+        model = Model.from_dir(model_dirs[name], dtype=dtype)
+        if not native:
+            for b in model.blocks:
+                b._native_layer = lambda: None
+        else:
+            assert all(b._native_layer() is not None for b in model.blocks)
+        eng = Engine(model, max_tokens=4096, use_graphs=False)
+        slots = [eng.new_sequence() for _ in prompts]
+        got = [eng.step(list(zip(slots, prompts)), [list(range(len(p))) for p in prompts])]
+        for s in range(2):
+            got.append(eng.step([(slot, [int(follow[s, i])]) for i, slot in enumerate(slots)]))     # 20 rows
+        for s in range(2, 4):
+            got.append(eng.step([(slot, [int(follow[s, i])]) for i, slot in enumerate(slots[:5])]))  # 5 rows
+        outs.append([g.clone() for g in got])
+        from gophonic_b200 import ops
+        assert ops.tc5_status() == 0
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
 def test_where_a_sequence_lies_in_the_cache_changes_nothing(engines, plain_models):
     eng = engines("A", "float32", 1024)
     cfg, _ = plain_models["A"]
