@@ -90,7 +90,7 @@ def test_swiglu(ops, dtype, inter):
 
 
 @pytest.mark.parametrize("M", [1, 8, 9, 33, 64, 100, 128, 300])
-@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (1000, 96), (12288 // 8, 512), (4096, 2048)])  # the last: K slices
+@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (1000, 96), (12288 // 8, 512), (4096, 2048), (9600, 1024)])  # the last two: K slices
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
     """gate/up rows interleaved in blocks of eight; the few-row kernel applies silu(gate) * up itself,
@@ -235,7 +235,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
 
 @pytest.mark.parametrize("algo", ["skinny", "tc5", "tc5_pair", "tc5_decode"])
 @pytest.mark.parametrize("M,N,K", SHAPES + [(8, 4096, 1024), (64, 1536, 2048), (100, 1536, 2048), (128, 200, 8200), (256, 4096, 520),
-                                            (300, 1000, 512), (2048, 512, 1024)])
+                                            (300, 1000, 512), (2048, 512, 1024), (48, 19200, 1024)])   # the last: more tiles than SMs
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tensor_core_kernels(ops, algo, M, N, K, out_dtype):
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
