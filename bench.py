@@ -26,13 +26,28 @@ sys.path.insert(0, ROOT)
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 
-# layer sizes by name: the default is the configuration the headline metric is quoted on; the
-# others are further points (--model), never the default
-SIZES = {
-    "8b": dict(layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, intermediate=12288, vocab=151936, tied=False),
-    "1.7b": dict(layers=28, hidden=2048, heads=16, kv_heads=8, head_dim=128, intermediate=6144, vocab=151936, tied=True),
-    "32b": dict(layers=64, hidden=5120, heads=64, kv_heads=8, head_dim=128, intermediate=25600, vocab=151936, tied=False),
-}
+# layer sizes by name, from the library's own configuration files: the default is the configuration
+# the headline metric is quoted on; the others are further points, never the default
+MODELS = ("8b", "1.7b", "32b")
+
+
+def sizes(name):
+    from gophonic_b200.config.presets import preset
+    c = preset(name)
+    return dict(layers=c["num_hidden_layers"], hidden=c["hidden_size"], heads=c["num_attention_heads"],
+                kv_heads=c["num_key_value_heads"], head_dim=c["head_dim"], intermediate=c["intermediate_size"],
+                vocab=c["vocab_size"], tied=bool(c["tie_word_embeddings"]))
+
+
+def config_of(name, layers, context):
+    """The named configuration with ``layers`` layers (0: all of them) and room for ``context`` positions."""
+    from gophonic_b200 import registry
+    from gophonic_b200.config.presets import preset
+    raw = dict(preset(name))
+    if layers:
+        raw["num_hidden_layers"] = layers
+    raw["max_position_embeddings"] = max(int(raw["max_position_embeddings"]), context)
+    return registry.config_class(registry.architecture_of(raw)).from_dict(raw)
 
 
 def peaks():
@@ -233,6 +248,37 @@ def time_prefill(engine, tokens, iters, warmup, torch):
     return statistics.median(times)
 
 
+def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
+    """Decode and prefill points of another named configuration (all its layers, random weights): 1.7B
+    at batch 1 and 8 to context 4096, 32B at batch 1 and 32 to context 8192, each with its prefill of
+    2,048 tokens; tokens a second and the fraction of the roofline, keyed by the model's name."""
+    from gophonic_b200.engine import Engine, Model
+    from gophonic_b200.sampling import DeviceSampler
+    context, batches = (8192, (1, 32)) if name == "32b" else (4096, (1, 8))
+    cfg = config_of(name, 0, context)
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    engine = Engine(model, max_tokens=max(batches) * context, max_slots=max(batches), max_seq_tokens=context)
+    fill_cache_random(engine, torch)
+    sampler = DeviceSampler(cfg.vocab_size, max(batches), engine.device)
+    weight_bytes, kv_bytes = model.weight_bytes_per_step(), engine.cache.bytes_per_token()
+    out = {}
+    for b in batches:
+        d = time_decode(engine, sampler, b, steps, 16, torch, ops)
+        out[f"{name}_decode_b{b}"] = round(b / (d["ms"] * 1e-3), 1)
+        out[f"{name}_decode_b{b}_hbm_frac"] = round((weight_bytes + kv_bytes * d["kv_tokens"]) / (d["ms"] * 1e-3) / 1e9 / hbm_peak, 4)
+    ms = time_prefill(engine, PREFILL_TOKENS, iters=3, warmup=2, torch=torch)
+    T = PREFILL_TOKENS
+    head_elems = cfg.vocab_size * cfg.hidden_size
+    head_bytes = head_elems * 2
+    params = (weight_bytes - head_bytes) // 2
+    flops = 2.0 * T * params + 2.0 * cfg.num_attention_heads * cfg.head_dim * T * T * cfg.num_hidden_layers + 2.0 * head_elems
+    out[f"{name}_prefill_tok_s"] = round(T / (ms * 1e-3), 1)
+    out[f"{name}_prefill_frac"] = round(flops / (ms * 1e-3) / (tflops_peak * 1e12), 4)
+    del engine, sampler, model
+    torch.cuda.empty_cache()
+    return out
+
+
 def probe(name):
     """Run one kernel of the step a few times on a small, fixed workload (operands larger than L2
     where the kernel is bound by memory), for profilers.  Prints the kernel's own timing."""
@@ -390,7 +436,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--points", default="1,64", help="batch sizes of the further decode points (default 1,64)")
-    ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes (default: the benchmark's own, 8b)")
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS), help="layer sizes (default: the benchmark's own, 8b)")
+    ap.add_argument("--extra-models", default="1.7b,32b",
+                    help="further sizes whose decode and prefill points go into \"points\" (default 1.7b,32b; '' for none)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length each sequence is filled to")
     ap.add_argument("--mixed", action="store_true",
                     help="instead of the headline run: 16 prompts of 64 to 2048 tokens that start together, then 256 tokens each, "
@@ -413,18 +461,14 @@ def main():
 
     import torch
     from gophonic_b200 import ops
-    from gophonic_b200.config import Qwen3Config
     from gophonic_b200.engine import Engine, Model
     from gophonic_b200.sampling import DeviceSampler
 
-    sz = SIZES[args.model]
+    sz = sizes(args.model)
     context = args.context
     full_layers = sz["layers"]
     layers = args.layers or full_layers
-    cfg = Qwen3Config(hidden_size=sz["hidden"], num_hidden_layers=layers, num_attention_heads=sz["heads"],
-                      num_key_value_heads=sz["kv_heads"], head_dim=sz["head_dim"], intermediate_size=sz["intermediate"],
-                      vocab_size=sz["vocab"], max_position_embeddings=max(40960, context), rms_norm_eps=1e-6, rope_theta=1e6,
-                      tie_word_embeddings=sz["tied"])
+    cfg = config_of(args.model, args.layers, context)
     hbm_peak, tflops_peak, which = peaks()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     if args.mixed:
@@ -441,6 +485,8 @@ def main():
     weight_bytes = model.weight_bytes_per_step()
     kv_bytes_per_token = engine.cache.bytes_per_token()
 
+    clocks_all = ClockSampler()      # over everything that is timed; ``clocks`` is the headline loop alone
+    clocks_all.start()
     clocks = ClockSampler()
     clocks.start()
     dev = time_decode(engine, sampler, args.batch, args.steps, warmup, torch, ops)
@@ -457,6 +503,14 @@ def main():
     torch.cuda.empty_cache()
     # the generator prefills its own long prompts first (see above): 16 untimed steps here too
     e2e = time_entry_point(model, args.batch, args.steps, max(warmup, 16), context, torch)
+
+    extra_points = {}
+    if not args.no_points and args.model == "8b" and not args.layers:
+        del model
+        torch.cuda.empty_cache()
+        for name in [m for m in args.extra_models.split(",") if m]:
+            extra_points.update(further_model_points(name, args.steps, torch, ops, hbm_peak, tflops_peak))
+    clock_all_info = clocks_all.stop()
 
     step_bytes = weight_bytes + kv_bytes_per_token * dev["kv_tokens"]
     achieved = step_bytes / (dev["ms"] * 1e-3) / 1e9
@@ -479,11 +533,13 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
                      "frac": round(achieved / hbm_peak, 4)},
     }
+    line["clocks_all"] = clock_all_info
     if not args.no_points:
         ms = prefill_ms
         T = PREFILL_TOKENS
-        params = (weight_bytes - model.head.numel() * model.head.element_size()) // 2
-        flops = 2.0 * T * params + 2.0 * cfg.num_attention_heads * cfg.head_dim * T * T * layers + 2.0 * model.head.numel()
+        head_elems = cfg.vocab_size * cfg.hidden_size
+        params = (weight_bytes - head_elems * 2) // 2
+        flops = 2.0 * T * params + 2.0 * cfg.num_attention_heads * cfg.head_dim * T * T * layers + 2.0 * head_elems
         line["prefill"] = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
                            "frac": round(flops / (ms * 1e-3) / (tflops_peak * 1e12), 4)}
         points = {}
@@ -491,6 +547,7 @@ def main():
             points[f"decode_b{b}"] = round(b / (d["ms"] * 1e-3), 1)
             bytes_b = weight_bytes + kv_bytes_per_token * d["kv_tokens"]
             points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (d["ms"] * 1e-3) / 1e9 / hbm_peak, 4)
+        points.update(extra_points)
         line["points"] = points
     print(json.dumps(line))
     return 0

@@ -147,7 +147,9 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
            cudaStream_t stream) {
     int steps = ceil_div(K, 32);
     // Few weight tiles (narrow outputs) leave SMs short of loads in flight: give each CTA more warps.
-    const int max_kw = (ceil_div(N, 16) <= 320 && MT <= 4) ? 16 : 8;
+    // See skinny_warps() in mma.cuh.
+    int max_kw = skinny_warps(ceil_div(N, 16));
+    if (MT > 4 && max_kw > 8) max_kw = 8;  // many batch rows: the accumulators take the registers of the second CTA
     int kw = 1;
     while (kw < max_kw && steps / (kw * 2) >= MIN_STEPS) kw *= 2;
     int k_per_warp = ceil_div(steps, kw) * 32;

@@ -206,7 +206,7 @@ struct FoldArgs {
 template <bool SCALED, int EPI>
 int launch(const FoldArgs& a, cudaStream_t stream) {
     const int steps = ceil_div(a.K, 32);
-    const int max_kw = ceil_div(a.N, 16) <= 320 ? 16 : 8;
+    const int max_kw = skinny_warps(ceil_div(a.N, 16));
     int kw = 1;
     while (kw < max_kw && steps / (kw * 2) >= MIN_STEPS) kw *= 2;
     const int k_per_warp = ceil_div(steps, kw) * 32;

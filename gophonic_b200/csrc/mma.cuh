@@ -58,3 +58,11 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+
+// Warps a CTA of the fragment-streaming products gets at most (they split K), for `tiles` CTAs of 16
+// weight rows: few tiles (narrow outputs) leave SMs short of loads in flight, so their CTAs get 16
+// warps, wide outputs 8.  Timed alone in chains of the same product, a rule that keeps every CTA
+// resident at once (16 warps up to two tiles an SM, 8 up to four, 4 up to eight) looked better at
+// the 32B sizes (320 tiles x K 25600: 57.7 -> 49.3 us; 640 x 5120: 23.1 -> 21.0), but inside the
+// decode step, between its other kernels, the same rule cost 40 us a layer; the step decides.
+static inline int skinny_warps(int tiles) { return tiles <= 320 ? 16 : 8; }
