@@ -66,3 +66,29 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 // the 32B sizes (320 tiles x K 25600: 57.7 -> 49.3 us; 640 x 5120: 23.1 -> 21.0), but inside the
 // decode step, between its other kernels, the same rule cost 40 us a layer; the step decides.
 static inline int skinny_warps(int tiles) { return tiles <= 320 ? 16 : 8; }
+
+// SMs of the current device (asked once per device).
+static inline int gb_sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// Whether a fragment-streaming product of `tiles` CTAs of `kw` warps is launched as a programmatic
+// dependent launch (its CTAs become resident and request their first weights while the kernel ahead
+// still runs).  Not when its last wave is thin: two CTAs of 16 warps or four of 8 fit an SM, and a
+// grid that fills these places once and leaves a few CTAs over (the 32B sizes: 320 tiles of 16
+// warps on 296 places, 640 of 8 on 592) ran a decode step of sixteen 32B layers in 4.50 ms as
+// dependent launches and in 3.61 ms as ordinary ones, at one sequence (4.87 and 4.26 ms at eight).
+// Grids of one wave, or with a well-filled last wave (the 8B and 1.7B sizes), gain 1-2 % as dependents.
+static inline bool skinny_dependent(int tiles, int kw) {
+    const int places = (kw >= 16 ? 2 : 4) * gb_sm_count();
+    const int last = tiles % places;
+    return tiles <= places || last == 0 || 4 * last >= places;
+}
