@@ -154,10 +154,10 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
     while (kw < max_kw && steps / (kw * 2) >= MIN_STEPS) kw *= 2;
     int k_per_warp = ceil_div(steps, kw) * 32;
     size_t smem = (size_t)kw * 16 * MT * 8 * sizeof(float);
-    // a programmatic dependent launch: the kernel requests its first weights before it waits for
-    // the kernel ahead of it
-    const bool one_wave = skinny_dependent(ceil_div(N, 16), kw);
-    cudaError_t e = launch_maybe_pdl(one_wave, gemm_skinny_kernel<MT>, dim3(ceil_div(N, 16)), dim3(kw * 32), smem, stream, (const __nv_bfloat16*)X,
+    // as a programmatic dependent launch the kernel requests its first weights before it waits for the
+    // kernel ahead of it; see skinny_dependent() for when it is one
+    const bool dependent = skinny_dependent(ceil_div(N, 16));
+    cudaError_t e = launch_maybe_pdl(dependent, gemm_skinny_kernel<MT>, dim3(ceil_div(N, 16)), dim3(kw * 32), smem, stream, (const __nv_bfloat16*)X,
                                (const __nv_bfloat16*)W, Y, (int)(c_dtype == GB_BF16), M, N, K, ldx, ldy, k_per_warp, epi);
     if (e != cudaSuccess) GB_REFUSE("gemm_skinny: launch failed: %s", cudaGetErrorString(e));
     return 0;

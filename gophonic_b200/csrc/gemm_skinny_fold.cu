@@ -211,8 +211,8 @@ int launch(const FoldArgs& a, cudaStream_t stream) {
     while (kw < max_kw && steps / (kw * 2) >= MIN_STEPS) kw *= 2;
     const int k_per_warp = ceil_div(steps, kw) * 32;
     const size_t smem = (size_t)kw * 16 * 8 * sizeof(float);
-    const bool one_wave = skinny_dependent(ceil_div(a.N, 16), kw);
-    cudaError_t e = launch_maybe_pdl(one_wave, gemm_skinny_fold_kernel<SCALED, EPI>, dim3(ceil_div(a.N, 16)), dim3(kw * 32), smem, stream,
+    const bool dependent = skinny_dependent(ceil_div(a.N, 16));
+    cudaError_t e = launch_maybe_pdl(dependent, gemm_skinny_fold_kernel<SCALED, EPI>, dim3(ceil_div(a.N, 16)), dim3(kw * 32), smem, stream,
                                (const __nv_bfloat16*)a.X, a.ldx, a.stats_in, a.stats_count, a.stats_in_stride, a.eps,
                                (const __nv_bfloat16*)a.W, a.Y, (int)(a.y_dtype == GB_BF16), a.ldy, a.stats_out, a.stats_out_stride,
                                a.next_w, (__nv_bfloat16*)a.xn_out, a.ldxn, a.M, a.N, a.K, k_per_warp);

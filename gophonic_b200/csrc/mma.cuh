@@ -59,14 +59,6 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return v;
 }
 
-// Warps a CTA of the fragment-streaming products gets at most (they split K), for `tiles` CTAs of 16
-// weight rows: few tiles (narrow outputs) leave SMs short of loads in flight, so their CTAs get 16
-// warps, wide outputs 8.  Timed alone in chains of the same product, a rule that keeps every CTA
-// resident at once (16 warps up to two tiles an SM, 8 up to four, 4 up to eight) looked better at
-// the 32B sizes (320 tiles x K 25600: 57.7 -> 49.3 us; 640 x 5120: 23.1 -> 21.0), but inside the
-// decode step, between its other kernels, the same rule cost 40 us a layer; the step decides.
-static inline int skinny_warps(int tiles) { return tiles <= 320 ? 16 : 8; }
-
 // SMs of the current device (asked once per device).
 static inline int gb_sm_count() {
     static int cached[64];
@@ -80,15 +72,35 @@ static inline int gb_sm_count() {
     return cached[dev];
 }
 
-// Whether a fragment-streaming product of `tiles` CTAs of `kw` warps is launched as a programmatic
-// dependent launch (its CTAs become resident and request their first weights while the kernel ahead
-// still runs).  Not when its last wave is thin: two CTAs of 16 warps or four of 8 fit an SM, and a
-// grid that fills these places once and leaves a few CTAs over (the 32B sizes: 320 tiles of 16
-// warps on 296 places, 640 of 8 on 592) ran a decode step of sixteen 32B layers in 4.50 ms as
-// dependent launches and in 3.61 ms as ordinary ones, at one sequence (4.87 and 4.26 ms at eight).
-// Grids of one wave, or with a well-filled last wave (the 8B and 1.7B sizes), gain 1-2 % as dependents.
-static inline bool skinny_dependent(int tiles, int kw) {
-    const int places = (kw >= 16 ? 2 : 4) * gb_sm_count();
-    const int last = tiles % places;
-    return tiles <= places || last == 0 || 4 * last >= places;
+// How a fragment-streaming product of `tiles` CTAs of 16 weight rows is launched: the most warps a
+// CTA gets (they split K), and whether it is a programmatic dependent launch (its CTAs become
+// resident and request their first weights while the kernel ahead still runs).  At 64 registers a
+// thread an SM holds two CTAs of 16 warps, four of 8 or eight of 4.  Few tiles (narrow outputs)
+// leave SMs short of loads in flight, so their CTAs get more warps; a product whose CTAs are not all
+// resident at once ends in a thin wave that costs as much as a full one.  Measured inside decode
+// steps of the 1.7B, 8B and 32B sizes (alone, in chains of the same product, the picture differs:
+// the step decides):
+//   up to two tiles an SM (8B output and down projections, 256 tiles): 16 warps, dependent;
+//   up to 320 tiles (32B output and down projections): 8 warps, ordinary launch; with 16 warps
+//     they leave 24 CTAs for a second wave, and as dependents of 8 warps they cost a third more;
+//   up to four tiles an SM (8B q/k/v, 384 tiles): 8 warps, dependent;
+//   up to eight (32B q/k/v, 640; 1.7B gate/up, 768): 4 warps, ordinary launch;
+//   wider (8B gate/up, 1536): 8 warps, dependent.
+// Against 16 warps up to 320 tiles, 8 beyond, all dependents: sixteen 32B layers at one sequence
+// 4.50 -> 3.26 ms (eight: 4.87 -> 3.62), 1.7B 1.30 -> 1.26 ms, 8B unchanged.
+static inline int skinny_warps(int tiles) {
+    const int sms = gb_sm_count();
+    if (tiles <= 2 * sms) return 16;
+    if (tiles <= 4 * sms) return 8;
+    if (tiles <= 8 * sms) return 4;
+    return 8;
+}
+
+static inline bool skinny_dependent(int tiles) {
+    const int sms = gb_sm_count();
+    if (tiles <= 2 * sms) return true;
+    if (tiles <= 320) return false;
+    if (tiles <= 4 * sms) return true;
+    if (tiles <= 8 * sms) return false;
+    return true;
 }
