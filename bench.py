@@ -279,7 +279,7 @@ def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
     return out
 
 
-def probe(name):
+def probe(name, **opts):
     """Run one kernel of the step a few times on a small, fixed workload (operands larger than L2
     where the kernel is bound by memory), for profilers.  Prints the kernel's own timing."""
     import torch
@@ -368,29 +368,28 @@ def probe(name):
         else:
             work, unit = 2.0 * heads * d * q_len * q_len, "TFLOP/s"
     elif name in ("prefill_step", "decode_step"):
-        # a whole engine step of a 4-layer model with the layer sizes of the benchmark: the launch
-        # list of a profiler then shows every kernel of a layer with its share
-        from gophonic_b200.config import Qwen3Config
+        # a whole engine step of a 4-layer model with the layer sizes of the benchmark (or of --model):
+        # the launch list of a profiler then shows every kernel of a layer with its share.  --batch
+        # and --context set the decode step's sequences and their length, --prompt-tokens the prompt.
         from gophonic_b200.engine import Engine, Model
-        cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=8,
-                          head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=40960,
-                          rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+        batch, context, tokens = opts.get("batch", 8), opts.get("context", CONTEXT), opts.get("prompt_tokens", PREFILL_TOKENS)
+        cfg = config_of(opts.get("model", "8b"), 4, context)
         model = Model.from_random(cfg, seed=0, dtype="bfloat16", device=dev)
-        engine = Engine(model, max_tokens=8 * CONTEXT, max_slots=8, max_seq_tokens=CONTEXT)
-        prompt = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(1)).tolist()
+        engine = Engine(model, max_tokens=batch * context, max_slots=batch, max_seq_tokens=context)
+        prompt = torch.randint(0, cfg.vocab_size, (tokens,), generator=torch.Generator().manual_seed(1)).tolist()
         if name == "prefill_step":
             def fn():
                 slot = engine.new_sequence()
                 engine.step([(slot, prompt)])
                 engine.end_sequence(slot)
-            work, unit = float(PREFILL_TOKENS), "tok/s"
+            work, unit = float(tokens), "tok/s"
         else:
             fill_cache_random(engine, torch)
-            slots = decode_setup(engine, 8, CONTEXT - 64, torch)
+            slots = decode_setup(engine, batch, context - 64, torch)
 
             def fn():
                 engine.step([(s, [1]) for s in slots])
-            work, unit = 8.0, "tok/s"
+            work, unit = float(batch), "tok/s"
     else:
         raise SystemExit(f"unknown probe '{name}'")
     for _ in range(3):
@@ -445,9 +444,10 @@ def main():
                          "through the entry point (a further point, with --model)")
     ap.add_argument("--profile", action="store_true", help="time each hot kernel alone and print its fraction of the roofline")
     ap.add_argument("--probe", default="", help="run one kernel on a small fixed workload (for profilers) and exit")
+    ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="prompt length of --probe prefill_step")
     args = ap.parse_args()
     if args.probe:
-        return probe(args.probe)
+        return probe(args.probe, model=args.model, batch=args.batch, context=args.context, prompt_tokens=args.prompt_tokens)
     if args.profile:
         return profile()
     if args.impl == "reference":
