@@ -3,13 +3,13 @@
 Importing the package needs no GPU.  The kernel library is compiled and loaded the first time a
 model is opened on a CUDA device.
 """
-from . import registry
+from . import chat, registry
 from .api import (ChatGeneratorLane, ChatOptions, Detect, ErrUnknownFormat, ErrUnsupported, Format, FormatBF16, FormatF32, Formats,
-                  Lane, Open, OpenedModel, Options, Provide, Register, Supports, TokensGenerator)
+                  Lane, Open, OpenedModel, Options, Provide, Register, Supports, TokensGenerator, random_model_path)
 from .config import ConfigError, Qwen3Config
 
 __version__ = "0.1.0"
 
 __all__ = ["ChatGeneratorLane", "ChatOptions", "ConfigError", "Detect", "ErrUnknownFormat", "ErrUnsupported", "Format", "FormatBF16",
            "FormatF32", "Formats", "Lane", "Open", "OpenedModel", "Options", "Provide", "Qwen3Config", "Register",
-           "Supports", "TokensGenerator", "registry"]
+           "Supports", "TokensGenerator", "chat", "random_model_path", "registry"]
