@@ -32,6 +32,8 @@ struct AttnParams {
     int window;
     int num_splits;
     float* scratch;  // [nseq][heads][num_splits][d + 2] when num_splits > 1
+    int pages;       // pages of each cache plane, and slots (rows) of the block table: the bounds the
+    int max_slots;   // checked build holds every page and slot index against
 };
 
 // Per-head q/k RMSNorm, rotary embedding and cache write on the rows of a fused q|k|v buffer.
@@ -54,6 +56,8 @@ struct QkRopeParams {
     void* v_plane;
     int write_kv;
     int rows, heads, kv_heads, d;
+    int pages;      // pages of each cache plane, and slots (rows) of the block table: the bounds the
+    int max_slots;  // checked build holds every page and slot index against
 };
 
 GB_API const char* gb_last_error();

@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
     const int past = kv_len - q_len;
     const int q_start = p.seq_q_start[seq];
     const int G = p.heads / p.kv_heads, kvh = head / G;
-    const int* bt = p.block_table + (int64_t)p.seq_slot[seq] * p.bt_stride;
+    const int* bt = block_table_row(p.block_table, p.bt_stride, p.seq_slot[seq], p.max_slots);
     const bf16* kbase = (const bf16*)p.k_plane;
     const bf16* vbase = (const bf16*)p.v_plane;
 
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
     const int t_lo = lo_pos / 64, t_hi = hi_pos / 64;
 
     auto load_tile = [&](int t, int buf) {
-        int64_t page = page_of(bt, t * 64);
+        int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
         load_page<HD>(Ks + buf * 64 * SD, kbase + off, tid, 128);
         load_page<HD>(Vs + buf * 64 * SD, vbase + off, tid, 128);
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
     const int kv_len = p.seq_kv_len[seq];
     const int q_row = p.seq_q_start[seq];
     const int pos = kv_len - 1;
-    const int* bt = p.block_table + (int64_t)p.seq_slot[seq] * p.bt_stride;
+    const int* bt = block_table_row(p.block_table, p.bt_stride, p.seq_slot[seq], p.max_slots);
     const bf16* kbase = (const bf16*)p.k_plane;
     const bf16* vbase = (const bf16*)p.v_plane;
     const int h0 = kvh * G + chunk * GC;            // first head of this CTA
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
 
     auto load_tile = [&](int i) {
         int t = my_lo + i;
-        int64_t page = page_of(bt, t * 64);
+        int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
         bf16* st = KV + (i % DSTAGES) * STAGE;
         load_page<HD>(st, kbase + off, tid, 128);
@@ -504,3 +504,6 @@ GB_API int gb_attention_decode_mma(const AttnParams* pp, cudaStream_t stream) {
     GB_DISPATCH_HD(launch_decode)
     GB_REFUSE("attention_decode_mma: head_dim %d", p.d);
 }
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_attention_mma)

@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
     if (q0 >= q_len) return;
     const int past = kv_len - q_len;
     const int q_start = p.seq_q_start[seq];
-    const int* bt = p.block_table + (int64_t)p.seq_slot[seq] * p.bt_stride;
+    const int* bt = block_table_row(p.block_table, p.bt_stride, p.seq_slot[seq], p.max_slots);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // stage the query rows, scaled
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
             int j = warp * 8 + jj;
             int key = t * KT + j;
             if (key <= hi_pos) {
-                int64_t page = page_of(bt, key);
+                int64_t page = page_of(bt, key, p.bt_stride, p.pages);
                 int64_t off = ((page * p.kv_heads + kvh) * GB_PAGE + (key % GB_PAGE)) * (int64_t)d;
                 const T* kp = (const T*)p.k_plane + off;
                 const T* vp = (const T*)p.v_plane + off;
@@ -302,3 +302,6 @@ GB_API int gb_attention_simt(const AttnParams* pp, int dtype, cudaStream_t strea
     if (dtype == GB_BF16) return launch<__nv_bfloat16>(p, stream);
     GB_REFUSE("attention: unknown dtype %d", dtype);
 }
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_attention_simt)

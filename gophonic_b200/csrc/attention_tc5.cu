@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     const int past = kv_len - q_len;
     const int q_start = p.seq_q_start[seq];
     const int G = p.heads / p.kv_heads, kvh = head / G;
-    const int* bt = p.block_table + (int64_t)p.seq_slot[seq] * p.bt_stride;
+    const int* bt = block_table_row(p.block_table, p.bt_stride, p.seq_slot[seq], p.max_slots);
 
     // pages each group walks: from the first page any of its rows may see to the page of its last row
     int lo_pos = 0;
@@ -254,8 +254,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 mbar_expect_tx(&k_full[s], K_BYTES);
                 unsigned char* ks = KVs + (size_t)s * STAGE_BYTES;
                 int lp = t_lo + j;
-                if (lp >= p.bt_stride) lp = p.bt_stride - 1;
-                const int row = (bt[lp] * p.kv_heads + kvh) * 64;
+                if (!gb_check(lp, p.bt_stride, GB_CHECK_LOGICAL_PAGE) || lp >= p.bt_stride) lp = p.bt_stride - 1;
+                const int row = ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * p.kv_heads + kvh) * 64;
 #pragma unroll
                 for (int h = 0; h < 2; h++) tma_load_2d(ks + h * KPANEL, &map_k, h * 64, row, &k_full[s]);
                 issued = j + 1;
@@ -280,8 +280,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 mbar_expect_tx(&v_full[s], V_BYTES);
                 unsigned char* vs = KVs + (size_t)s * STAGE_BYTES + K_BYTES;
                 int lp = t_lo + j;
-                if (lp >= p.bt_stride) lp = p.bt_stride - 1;
-                const int row = (bt[lp] * p.kv_heads + kvh) * 64;
+                if (!gb_check(lp, p.bt_stride, GB_CHECK_LOGICAL_PAGE) || lp >= p.bt_stride) lp = p.bt_stride - 1;
+                const int row = ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * p.kv_heads + kvh) * 64;
 #pragma unroll
                 for (int h = 0; h < 2; h++) tma_load_2d(vs + h * KPANEL, &map_v, h * 64, row, &v_full[s]);
                 issued = j + 1;
@@ -576,3 +576,6 @@ GB_API int gb_attention_tc5_status() {
     if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
     return v;
 }
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_attention_tc5)

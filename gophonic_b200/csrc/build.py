@@ -9,6 +9,12 @@ While compiling, a line is printed every few seconds so a first call does not lo
 
 There is no fallback: if the library cannot be built or loaded, importing the kernel
 operations raises.
+
+With ``GOPHONIC_B200_CHECKED=1`` in the environment a second library is built and loaded instead,
+compiled with ``-DGB_CHECKED``: every index its kernels take into the block table, a cache plane,
+the embedding table or a token source is held against its bound first, and an index out of bounds
+is recorded (``ops.checked_status()``) and not used.  It is the stand-in for a memory checker where
+none can be run, and costs a few per cent.
 """
 from __future__ import annotations
 
@@ -27,6 +33,8 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libgophonic_b200.so"
+CHECKED_LIB_NAME = "libgophonic_b200_checked.so"
+CHECKED_FLAG = "-DGB_CHECKED"
 
 SOURCES = [
     "elementwise.cu",
@@ -71,13 +79,17 @@ def _nvcc() -> str:
                      "(looked at $GOPHONIC_B200_NVCC, PATH and /usr/local/cuda/bin/nvcc)")
 
 
-def _digest() -> str:
+def checked_requested() -> bool:
+    return os.environ.get("GOPHONIC_B200_CHECKED", "") not in ("", "0")
+
+
+def _digest(flags: Optional[List[str]] = None) -> str:
     h = hashlib.sha256()
     for name in _existing(SOURCES) + _existing(HEADERS):
         h.update(name.encode())
         with open(os.path.join(HERE, name), "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + (flags or [])).encode())
     return h.hexdigest()
 
 
@@ -107,9 +119,9 @@ def build_dir() -> str:
     raise BuildError(f"neither {in_tree} nor {fallback} can be written; set GOPHONIC_B200_BUILD_DIR")
 
 
-def _up_to_date(bdir: str, digest: str) -> bool:
-    lib = os.path.join(bdir, LIB_NAME)
-    stamp = os.path.join(bdir, "stamp.json")
+def _up_to_date(bdir: str, digest: str, lib_name: str = LIB_NAME) -> bool:
+    lib = os.path.join(bdir, lib_name)
+    stamp = os.path.join(bdir, lib_name + ".stamp.json" if lib_name != LIB_NAME else "stamp.json")
     if not (os.path.exists(lib) and os.path.exists(stamp)):
         return False
     try:
@@ -124,20 +136,25 @@ def _say(msg: str, verbose: bool) -> None:
         print(f"[gophonic_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def ensure_built(verbose: bool = True, extra_flags: Optional[List[str]] = None) -> str:
-    """Compile the library if it is missing or stale; return its path."""
-    digest = _digest()
+def ensure_built(verbose: bool = True, extra_flags: Optional[List[str]] = None, checked: bool = False) -> str:
+    """Compile the library if it is missing or stale; return its path.  ``checked``: the library with
+    bounds-checked indices, kept beside the ordinary one."""
+    extra = list(extra_flags or []) + ([CHECKED_FLAG] if checked else [])
+    lib_name = CHECKED_LIB_NAME if checked else LIB_NAME
+    stamp_name = lib_name + ".stamp.json" if checked else "stamp.json"
+    digest = _digest(extra)
     # an up-to-date library anywhere we would build is used as it is
     in_tree = os.path.join(HERE, "_build")
-    if not os.environ.get("GOPHONIC_B200_BUILD_DIR") and _up_to_date(in_tree, digest):
-        return os.path.join(in_tree, LIB_NAME)
+    if not os.environ.get("GOPHONIC_B200_BUILD_DIR") and _up_to_date(in_tree, digest, lib_name):
+        return os.path.join(in_tree, lib_name)
     bdir = build_dir()
-    if _up_to_date(bdir, digest):
-        return os.path.join(bdir, LIB_NAME)
+    if _up_to_date(bdir, digest, lib_name):
+        return os.path.join(bdir, lib_name)
     nvcc = _nvcc()
     sources = _existing(SOURCES)
-    flags = NVCC_FLAGS + (extra_flags or [])
-    _say(f"compiling {len(sources)} CUDA sources for sm_100a into {bdir} (first call only)", verbose)
+    flags = NVCC_FLAGS + extra
+    _say(f"compiling {len(sources)} CUDA sources for sm_100a into {bdir} (first call only"
+         f"{'; the build with checked indices' if checked else ''})", verbose)
     t0 = time.time()
     done = threading.Event()
 
@@ -163,13 +180,13 @@ def ensure_built(verbose: bool = True, extra_flags: Optional[List[str]] = None) 
         workers = max(1, min(len(sources), os.cpu_count() or 1))
         with concurrent.futures.ThreadPoolExecutor(max_workers=workers) as ex:
             objs = list(ex.map(compile_one, sources))
-        tmp_lib = os.path.join(bdir, f"{LIB_NAME}.{tag}.tmp")
+        tmp_lib = os.path.join(bdir, f"{lib_name}.{tag}.tmp")
         cmd = [nvcc, "-shared", "-o", tmp_lib] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise BuildError(f"linking the kernel library failed:\n{r.stdout}")
-        os.replace(tmp_lib, os.path.join(bdir, LIB_NAME))
-        with open(os.path.join(bdir, "stamp.json"), "w") as f:
+        os.replace(tmp_lib, os.path.join(bdir, lib_name))
+        with open(os.path.join(bdir, stamp_name), "w") as f:
             json.dump({"digest": digest, "flags": flags, "sources": sources}, f)
     finally:
         done.set()
@@ -181,7 +198,7 @@ def ensure_built(verbose: bool = True, extra_flags: Optional[List[str]] = None) 
                 except OSError:
                     pass
     _say(f"kernel library ready after {time.time() - t0:.0f} s", verbose)
-    return os.path.join(bdir, LIB_NAME)
+    return os.path.join(bdir, lib_name)
 
 
 _lib: Optional[ctypes.CDLL] = None
@@ -193,7 +210,7 @@ def load(verbose: bool = True) -> ctypes.CDLL:
     global _lib
     with _lib_lock:
         if _lib is None:
-            path = ensure_built(verbose=verbose)
+            path = ensure_built(verbose=verbose, checked=checked_requested())
             try:
                 _lib = ctypes.CDLL(path)
             except OSError as e:

@@ -12,7 +12,9 @@ __global__ void block_table_set_kernel(int* __restrict__ table, int bt_stride, i
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int slot = triples[3 * i], lp = triples[3 * i + 1], page = triples[3 * i + 2];
-    if (slot < 0 || slot >= max_slots || lp < 0 || lp >= bt_stride) return;  // checked on the host; never out of bounds
+    // checked on the host; never out of bounds
+    if (!gb_check(slot, max_slots, GB_CHECK_TRIPLE) || !gb_check(lp, bt_stride, GB_CHECK_TRIPLE)) return;
+    if (slot < 0 || slot >= max_slots || lp < 0 || lp >= bt_stride) return;
     table[(int64_t)slot * bt_stride + lp] = page;
 }
 
@@ -27,7 +29,7 @@ GB_API int gb_block_table_set(int* table, int bt_stride, int max_slots, const in
 __global__ void zero_pages_kernel(unsigned char* __restrict__ base, int64_t plane_stride, int64_t page_bytes, int n_pages,
                                   const int* __restrict__ triples) {
     const int page = triples[3 * blockIdx.x + 2];
-    if (page < 0 || page >= n_pages) return;
+    if (!gb_check(page, n_pages, GB_CHECK_TRIPLE) || page < 0 || page >= n_pages) return;
     uint4* dst = reinterpret_cast<uint4*>(base + (int64_t)blockIdx.y * plane_stride + (int64_t)page * page_bytes);
     const int64_t n16 = page_bytes >> 4;
     for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -89,3 +91,6 @@ GB_API int gb_random_fill(void* out, int dtype, int64_t n, unsigned long long ke
     GB_CHECK_LAUNCH("random_fill");
     return 0;
 }
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_cache)

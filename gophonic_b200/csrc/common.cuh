@@ -59,8 +59,65 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Physical page of token `pos` of the sequence whose block-table row is `bt`.
-__device__ __forceinline__ int64_t page_of(const int* __restrict__ bt, int pos) { return (int64_t)bt[pos / GB_PAGE]; }
+// The checked build (compiled with -DGB_CHECKED; the stand-in for a memory checker where none can be
+// run): every index that reaches the block table, a cache plane, the embedding table or a token
+// source is compared with its bound first.  An index out of bounds is recorded (the first one with
+// its value and bound, and a count of all) in a status word of the translation unit, and the
+// access is skipped or redirected to element 0, so the kernel neither faults nor reads what it should
+// not.  The host reads the words of all translation units with gb_checked_status().  In the
+// ordinary build the checks compile to nothing.
+enum GbCheckCode : int {
+    GB_CHECK_TOKEN_ID = 1,       // a token id outside the vocabulary
+    GB_CHECK_TOKEN_SOURCE = 2,   // a position outside the token source
+    GB_CHECK_SLOT = 3,           // a cache slot outside the block table
+    GB_CHECK_LOGICAL_PAGE = 4,   // a position beyond the pages a block-table row has
+    GB_CHECK_PHYSICAL_PAGE = 5,  // a block-table entry outside the cache plane
+    GB_CHECK_ROPE_POSITION = 6,  // a position beyond the rotation tables
+    GB_CHECK_KV_LENGTH = 7,      // a sequence longer than its block-table row can hold, or shorter than its new rows
+    GB_CHECK_TRIPLE = 8,         // a (slot, logical, physical) triple outside the table or the plane
+};
+#ifdef GB_CHECKED
+static __device__ int gb_check_word[4];  // first code, its value, its bound, count of all
+__device__ __forceinline__ bool gb_check(long long v, long long bound, int code) {
+    if (v >= 0 && v < bound) return true;
+    if (atomicCAS(&gb_check_word[0], 0, code) == 0) {
+        gb_check_word[1] = (int)v;
+        gb_check_word[2] = (int)bound;
+    }
+    atomicAdd(&gb_check_word[3], 1);
+    return false;
+}
+#define GB_CHECK_READER(name)                                                                           \
+    GB_API int name(int* out4) {                                                                        \
+        int zero[4] = {0, 0, 0, 0};                                                                     \
+        if (cudaMemcpyFromSymbol(out4, gb_check_word, sizeof(zero)) != cudaSuccess) return -1;          \
+        if (out4[0] != 0 || out4[3] != 0) cudaMemcpyToSymbol(gb_check_word, zero, sizeof(zero));        \
+        return out4[0];                                                                                 \
+    }
+#else
+__device__ __forceinline__ bool gb_check(long long, long long, int) { return true; }
+#define GB_CHECK_READER(name)                      \
+    GB_API int name(int* out4) {                   \
+        out4[0] = out4[1] = out4[2] = out4[3] = 0; \
+        return 0;                                  \
+    }
+#endif
+
+// Physical page of token `pos` of the sequence whose block-table row is `bt` (bt_stride entries), in
+// a plane of `pages` pages.
+__device__ __forceinline__ int64_t page_of(const int* __restrict__ bt, int pos, int bt_stride, int pages) {
+    const int lp = pos / GB_PAGE;
+    if (!gb_check(lp, bt_stride, GB_CHECK_LOGICAL_PAGE)) return 0;
+    const int page = bt[lp];
+    if (!gb_check(page, pages, GB_CHECK_PHYSICAL_PAGE)) return 0;
+    return (int64_t)page;
+}
+
+// Block-table row of the cache slot a sequence lives in.
+__device__ __forceinline__ const int* block_table_row(const int* __restrict__ table, int bt_stride, int slot, int max_slots) {
+    if (!gb_check(slot, max_slots, GB_CHECK_SLOT)) slot = 0;
+    return table + (int64_t)slot * bt_stride;
+}
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

@@ -19,7 +19,16 @@ void gb_set_error(const char* fmt, ...) {
 
 GB_API const char* gb_last_error() { return g_error; }
 
-GB_API int gb_abi_version() { return 1; }
+GB_API int gb_abi_version() { return 2; }
+
+// 1 if the library was built with bounds-checked indices (see common.cuh)
+GB_API int gb_is_checked() {
+#ifdef GB_CHECKED
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 // ------------------------------------------------------------------------------------------
 // embedding: h[r, :] = float(table[ids[r], :])      (internal/qwen3lm/evaluator.go:594-599)
@@ -34,7 +43,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     int r = blockIdx.x;
     int id = ids[r];
     // ids are validated on the host; an id outside the table reads row 0 rather than faulting.
-    if (id < 0 || id >= vocab) id = 0;
+    if (!gb_check(id, vocab, GB_CHECK_TOKEN_ID) || id < 0 || id >= vocab) id = 0;
     const T* src = table + (int64_t)id * hidden;
     float* dst = out + (int64_t)r * hidden;
     float ss = 0.f;
@@ -80,6 +89,7 @@ __global__ void gather_tokens_kernel(int* __restrict__ ids, const int* __restric
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     int p = ids[i];
+    gb_check(p, source_n, GB_CHECK_TOKEN_SOURCE);
     ids[i] = (p >= 0 && p < source_n) ? source[p] : 0;
 }
 
@@ -345,7 +355,7 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     } else {
         if (!p.write_kv) return;
         int slot = p.seq_slot[p.row_seq[r]];
-        int64_t page = page_of(p.block_table + (int64_t)slot * p.bt_stride, pos);
+        int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot, p.max_slots), pos, p.bt_stride, p.pages);
         T* plane = (T*)(is_k ? p.k_plane : p.v_plane);
         dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)d;
     }
@@ -372,8 +382,9 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     __syncwarp();
     int half = p.rot / 2;
     // rows whose position lies beyond the table are refused on the host
-    const float* c = p.cos_t + (int64_t)pos * half;
-    const float* s = p.sin_t + (int64_t)pos * half;
+    const int tpos = (half == 0 || gb_check(pos, p.table_positions, GB_CHECK_ROPE_POSITION)) ? pos : 0;
+    const float* c = p.cos_t + (int64_t)tpos * half;
+    const float* s = p.sin_t + (int64_t)tpos * half;
     for (int i = lane; i < d; i += 32) {
         float v;
         if (i < half)
@@ -430,7 +441,7 @@ __global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) 
         }
 #pragma unroll
         for (int j = 0; j < ROPE_ROWS; j++) {
-            const int64_t page = page_of(p.block_table + (int64_t)slot[j] * p.bt_stride, pos[j]);
+            const int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot[j], p.max_slots), pos[j], p.bt_stride, p.pages);
             bf* plane = (bf*)(is_k ? p.k_plane : p.v_plane);
             dst[j] = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos[j] % GB_PAGE)) * (int64_t)128 + lane * 4;
         }
@@ -443,8 +454,9 @@ __global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) 
     }
 #pragma unroll
     for (int j = 0; j < ROPE_ROWS; j++) {
-        c[j] = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)pos[j] * 64 + ci);
-        sn[j] = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)pos[j] * 64 + ci);
+        const int tpos = gb_check(pos[j], p.table_positions, GB_CHECK_ROPE_POSITION) ? pos[j] : 0;
+        c[j] = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)tpos * 64 + ci);
+        sn[j] = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)tpos * 64 + ci);
     }
     float4 ww = make_float4(1.f, 1.f, 1.f, 1.f);
     if (w) ww = *reinterpret_cast<const float4*>(w + lane * 4);
@@ -519,3 +531,6 @@ GB_API int gb_f32_to_bf16(const float* a, void* b, int64_t n, cudaStream_t strea
     GB_CHECK_LAUNCH("f32_to_bf16");
     return 0;
 }
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_rows)

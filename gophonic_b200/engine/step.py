@@ -222,9 +222,16 @@ class Engine:
 
     def check_kernels(self) -> None:
         """Raise if a kernel recorded that it gave up waiting on a barrier (synchronises)."""
-        code = self.model.rt.ops.tc5_status()
+        ops = self.model.rt.ops
+        code = ops.tc5_status()
         if code:
             raise RuntimeError(f"a tcgen05 kernel gave up waiting on a barrier (role {code}); results are not valid")
+        if ops.is_checked_build():
+            found = ops.checked_status()
+            if found is not None:
+                where, what, value, bound, count = found
+                raise RuntimeError(f"a kernel ({where}) met {what}: {value} against a bound of {bound} ({count} in all); "
+                                   f"the accesses were skipped, results are not valid")
 
     def room(self) -> int:
         """Free pages of 64 tokens."""

@@ -433,6 +433,28 @@ def tc5_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     return K % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
+def is_checked_build() -> bool:
+    """Whether the loaded library was compiled with bounds-checked indices (GOPHONIC_B200_CHECKED=1)."""
+    return bool(_lib.gb_is_checked())
+
+
+_CHECK_NAMES = {1: "a token id outside the vocabulary", 2: "a position outside the token source", 3: "a cache slot outside the block table",
+                4: "a position beyond the pages of a block-table row", 5: "a block-table entry outside the cache plane",
+                6: "a position beyond the rotation tables", 7: "a sequence length that does not fit", 8: "a page triple outside the table or plane"}
+
+
+def checked_status():
+    """None, or (where, what, value, bound, count) for the first index a kernel of the checked build
+    found out of bounds since the last call (the access was skipped or redirected, nothing faulted).
+    Always None in the ordinary build, whose kernels carry no checks.  Synchronises."""
+    out = (c_int * 4)()
+    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5"):
+        code = int(getattr(_lib, "gb_checked_status_" + name)(out))
+        if code or out[3]:
+            return name, _CHECK_NAMES.get(code, f"code {code}"), out[1], out[2], out[3]
+    return None
+
+
 def tc5_status() -> int:
     """0, or which role of a tcgen05 kernel gave up waiting on a barrier since the last call."""
     code = 0
@@ -449,6 +471,7 @@ class _QkRopeParams(Structure):
         ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p), ("block_table", c_void_p),
         ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
         ("write_kv", c_int), ("rows", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
+        ("pages", c_int), ("max_slots", c_int),
     ]
 
 
@@ -489,7 +512,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim
                       table_positions, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                       block_table.data_ptr(), block_table.stride(0),
                       0 if k_plane is None else k_plane.data_ptr(), 0 if v_plane is None else v_plane.data_ptr(),
-                      1 if write_kv else 0, rows, heads, kv_heads, head_dim)
+                      1 if write_kv else 0, rows, heads, kv_heads, head_dim,
+                      0 if k_plane is None else k_plane.shape[0], block_table.shape[0])
     _check(_lib.gb_qk_norm_rope_kv_write(byref(p), _code(qkv.dtype), _stream()))
 
 
@@ -500,6 +524,7 @@ class _AttnParams(Structure):
         ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
         ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
+        ("pages", c_int), ("max_slots", c_int),
     ]
 
 
@@ -537,7 +562,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
     p = _AttnParams(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_plane.data_ptr(), v_plane.data_ptr(),
                     block_table.data_ptr(), block_table.stride(0), seq_slot.data_ptr(),
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
-                    head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr())
+                    head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr(),
+                    k_plane.shape[0], block_table.shape[0])
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
         algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
@@ -572,6 +598,7 @@ class _StepRows(Structure):
         ("rows", c_int), ("nseq", c_int), ("max_q_len", c_int), ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p),
         ("seq_q_start", c_void_p), ("seq_q_len", c_void_p), ("seq_kv_len", c_void_p), ("num_splits", c_int), ("split_scratch", c_void_p),
         ("block_table", c_void_p), ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p), ("pages", c_int), ("write_kv", c_int),
+        ("max_slots", c_int),
     ]
 
 
@@ -605,7 +632,7 @@ def prenorm_layer_forward(layer: PrenormLayer, batch, cache, h: torch.Tensor, de
     step = _StepRows(rows, batch.nseq, batch.max_q_len, batch.row_pos.data_ptr(), batch.row_seq.data_ptr(), batch.seq_slot.data_ptr(),
                      batch.seq_q_start.data_ptr(), batch.seq_q_len.data_ptr(), batch.seq_kv_len.data_ptr(), num_splits,
                      0 if split_scratch is None else split_scratch.data_ptr(), cache.block_table.data_ptr(), cache.block_table.stride(0),
-                     cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], 1 if cache.writable else 0)
+                     cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], 1 if cache.writable else 0, cache.block_table.shape[0])
     out_ptr, n = c_void_p(0), c_int(0)
     _check(_lib.gb_prenorm_layer_forward(byref(layer), byref(step), _ptr(h), _ptr(delta), _ptr(workspace), c_int64(workspace.numel()),
                                          c_int(_sms()), byref(out_ptr), byref(n), _stream()), 0)

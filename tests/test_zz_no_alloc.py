@@ -26,7 +26,8 @@ class Params(Structure):
                 ("k_plane", c_void_p), ("v_plane", c_void_p), ("block_table", c_void_p), ("bt_stride", c_int),
                 ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
                 ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
-                ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p)]
+                ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
+                ("pages", c_int), ("max_slots", c_int)]
 
 
 @pytest.fixture(scope="module")
@@ -52,7 +53,7 @@ def case(dtype, heads, kvh, d, kv_lens, splits, seed):
     out = torch.full((nseq, heads * d), float("nan"), dtype=dtype, device=DEV)
     p = Params(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k.data_ptr(), v.data_ptr(), table.data_ptr(),
                table.stride(0), meta["slot"].data_ptr(), meta["start"].data_ptr(), meta["qlen"].data_ptr(),
-               meta["kvlen"].data_ptr(), nseq, heads, kvh, d, 1, 1.0 / math.sqrt(d), 0, splits, 0)
+               meta["kvlen"].data_ptr(), nseq, heads, kvh, d, 1, 1.0 / math.sqrt(d), 0, splits, 0, n_pages, nseq)
     keep = (q, k, v, table, meta)
     return p, out, keep
 
