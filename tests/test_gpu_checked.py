@@ -36,7 +36,7 @@ DEV = "cuda:0"
 
 # ---- the engine's own steps trip nothing -----------------------------------------------------
 rng = np.random.default_rng(3)
-for name, dtype, tol in (("B", "float32", 1e-4), ("D", "bfloat16", 3e-2), ("F", "bfloat16", 3e-2)):
+for name, dtype, tol in (("B", "float32", 2e-5), ("D", "bfloat16", 2e-2), ("F", "bfloat16", 2e-2)):
     cfg = tiny_configs()[name]
     with tempfile.TemporaryDirectory() as d:
         write_random_model(cfg, 5, d, scales=InitScales(matrix=0.1, embedding=1.0, head=0.1, norm=0.1))

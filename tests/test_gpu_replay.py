@@ -3,10 +3,12 @@ cutting the work: each request alone and whole; with the last 32 tokens one by o
 of unequal lengths whose shorter requests end earlier, one batch after another so that slots and
 pages are used again; long decoding; the first tokens of a sequence; and through bin/trace_run.
 
-Tolerances (fixed here once): every logit within 1e-4 (32-bit) or 3e-2 (bfloat16) of the largest
+Tolerances (fixed here once): every logit within 2e-5 (32-bit) or 2e-2 (bfloat16) of the largest
 reference logit of the compared block; every row of logits with a cosine to the reference row of
-at least 0.999999 / 0.999; and the same greedy token wherever the reference's top two stand
-further apart than the tolerance.
+at least 0.9999999 / 0.9995; and the same greedy token wherever the reference's top two stand
+further apart than the tolerance.  (Measured on the tiny configurations: 32-bit errors up to
+1.5e-6, bfloat16 up to 1e-2 with cosines from 0.99994; the target this build was given for the
+32-bit path is 1e-4.)
 """
 import json
 import os
@@ -21,7 +23,7 @@ from tests.plain import qwen3_plain as P
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -29,7 +31,7 @@ def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
     return float(np.max(np.abs(got.astype(np.float64) - ref)) / np.max(np.abs(ref)))
 
 
-COSINE = {"float32": 0.999999, "bfloat16": 0.999}
+COSINE = {"float32": 0.9999999, "bfloat16": 0.9995}
 
 
 def first_bad_row(got: np.ndarray, ref: np.ndarray, dtype: str):
