@@ -82,6 +82,8 @@ GB_API int gb_gemm_tc5_pair(const void* A, const void* W, void* C, int c_dtype, 
 GB_API int gb_gemm_tc5_pair_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
                                    cudaStream_t stream);
 GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream);
+// most rows the products with the residual's row-wise work folded in take
+constexpr int GB_FOLD_MAX_ROWS = 64;
 GB_API int gb_gemm_tc5_decode_splits(int M, int N, int K, int sms);
 GB_API int gb_gemm_tc5_decode(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, int epi,
                               int splits, cudaStream_t stream);

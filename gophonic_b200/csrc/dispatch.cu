@@ -35,6 +35,7 @@ GB_API int gb_dispatch_constant(int which) {
         case 2: return TC5_PAIR_MIN_ROWS;
         case 3: return WIDE_OUTPUT;
         case 4: return TC5_ATTENTION_MIN_ROWS;
+        case 5: return GB_FOLD_MAX_ROWS;
     }
     return -1;
 }

@@ -142,7 +142,7 @@ class Model:
         schedule = self.spec.schedule
         first = self.blocks[schedule[0].layer]
         weight = None
-        if rows <= ops.STAT_ROWS and hasattr(first, "wants_stats") and first.wants_stats(rows):
+        if rows <= ops.FOLD_ROWS and hasattr(first, "wants_stats") and first.wants_stats(rows):
             weight = fold_weight(first.first_norm(), self.spec.hidden)
         if weight is not None:
             stats, prescaled = fold_buffers(batch, 0, self.spec.hidden)

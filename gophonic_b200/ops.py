@@ -265,19 +265,25 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str =
 
 
 # ---- few-row products with the residual's row-wise work folded in ------------------------
-STAT_ROWS = 8   # rows a statistics buffer holds; the folded products take up to this many rows
+FOLD_ROWS = int(_lib.gb_dispatch_constant(c_int(5)))   # the folded products take up to this many rows
+
+
+def fold_capacity(width: int) -> int:
+    """Partial sums a row that a statistics buffer must have room for when ``gemm_residual`` writes a
+    residual ``width`` wide: one per 16 columns (the kernel for more than 8 rows leaves one per 128)."""
+    return (width + 15) // 16
 
 
 def _skinny_operands_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= STAT_ROWS
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= FOLD_ROWS
             and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.is_contiguous() and w.data_ptr() % 16 == 0)
 
 
 def gemm_scaled_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether ``gemm_scaled`` takes this product: up to 8 bfloat16 rows against bfloat16 weights
-    whose rows are 16-byte aligned, an output narrower than the head's."""
-    return _skinny_operands_ok(x, w) and w.shape[0] < WIDE_OUTPUT
+    """Whether ``gemm_scaled`` takes this product: up to 64 bfloat16 rows against bfloat16 weights
+    whose rows are 16-byte aligned."""
+    return _skinny_operands_ok(x, w)
 
 
 def gemm_scaled(x: torch.Tensor, eps: float, stats: torch.Tensor, stats_count: int, w: torch.Tensor, out: torch.Tensor,
@@ -297,9 +303,15 @@ def gemm_scaled(x: torch.Tensor, eps: float, stats: torch.Tensor, stats_count: i
             or out.shape != (M, N // 2 if swiglu else N) or stats.shape[0] < M or not 0 < stats_count <= stats.shape[1]):
         raise KernelError(f"gemm_scaled: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
                           f"{stats_count} partial sums in {tuple(stats.shape)}")
-    _check(_lib.gb_gemm_skinny_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
-                                      c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
-                                      c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream()))
+    if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT:   # the kernels ``gemm`` picks: fragment streaming, else tcgen05 decode
+        _check(_lib.gb_gemm_skinny_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
+                                          c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
+                                          c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream()))
+        return
+    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sms())))
+    _check(_lib.gb_gemm_tc5_decode_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
+                                          c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
+                                          c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(splits), _stream()))
 
 
 def gemm_residual_accepts(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor) -> bool:
@@ -309,23 +321,31 @@ def gemm_residual_accepts(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor) -> 
 def gemm_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, stats: torch.Tensor,
                   next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None) -> int:
     """h += x @ w^T in place (``h`` float32: the residual stream; one float32 addition per element,
-    as a separate add gives) and stats[row, c] = the sum of squares of the 16 new values of the row
-    in columns 16 c .. 16 c + 15.  With ``next_weight`` also next_x = bf16(h * next_weight), the
-    rows ``gemm_scaled`` takes.  Returns the number of partial sums a row."""
+    as a separate add gives) and stats[row, c] = the sum of squares of the new values of the row
+    in the c-th block of columns (16 wide up to 8 rows, 128 wide above).  With ``next_weight`` also next_x = bf16(h * next_weight), the rows
+    ``gemm_scaled`` takes.  ``stats`` needs ``fold_capacity(N)`` columns.  Returns the number of
+    partial sums a row."""
     _need(x, "gemm a", torch.bfloat16, 2, contiguous=False)
     _need(w, "gemm w", torch.bfloat16, 2)
     _need(h, "residual", torch.float32, 2, contiguous=False)
     _need(stats, "row statistics", torch.float32, 2)
     M, K = x.shape
     N = w.shape[0]
-    count = (N + 15) // 16
+    count = fold_capacity(N)
     if not gemm_residual_accepts(x, w, h) or w.shape[1] != K or h.shape != (M, N) or stats.shape[0] < M or stats.shape[1] < count:
         raise KernelError(f"gemm_residual: x {tuple(x.shape)}, w {tuple(w.shape)}, h {tuple(h.shape)}, statistics {tuple(stats.shape)}")
     ldxn = _check_next(next_weight, next_x, M, N, "gemm_residual")
-    _check(_lib.gb_gemm_skinny_residual(_ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(h), c_int64(h.stride(0)), _ptr(stats),
-                                        c_int64(stats.stride(0)), _ptr(next_weight), _ptr(next_x), c_int64(ldxn),
-                                        c_int(M), c_int(N), c_int(K), _stream()))
-    return count
+    if M <= SKINNY_MAX_ROWS:
+        _check(_lib.gb_gemm_skinny_residual(_ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(h), c_int64(h.stride(0)), _ptr(stats),
+                                            c_int64(stats.stride(0)), _ptr(next_weight), _ptr(next_x), c_int64(ldxn),
+                                            c_int(M), c_int(N), c_int(K), _stream()))
+        return count
+    splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sms())))
+    made = c_int(0)
+    _check(_lib.gb_gemm_tc5_decode_residual(_ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(h), c_int64(h.stride(0)), _ptr(stats),
+                                            c_int64(stats.stride(0)), byref(made), _ptr(next_weight), _ptr(next_x), c_int64(ldxn),
+                                            c_int(M), c_int(N), c_int(K), c_int(splits), _stream()))
+    return made.value
 
 
 # ---- matrix products ---------------------------------------------------------------------

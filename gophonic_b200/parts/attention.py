@@ -126,12 +126,12 @@ class Attention(Mixer):
         self.rt.ops.gemm_add(self._context(batch, x, cache), self.o, h)
 
     def folds_norm(self, rows: int, norm) -> bool:
-        """Single-token steps of up to eight rows in bfloat16: the q/k/v product applies the rows'
+        """Steps of up to 64 rows in bfloat16: the q/k/v product applies the rows'
         norm factors from the residual's statistics and the output projection adds into the residual."""
         ops = self.rt.ops
-        return (rows <= ops.STAT_ROWS and self.rt.act_dtype == torch.bfloat16 and self.qkv.dtype == torch.bfloat16
+        return (rows <= ops.FOLD_ROWS and self.rt.act_dtype == torch.bfloat16 and self.qkv.dtype == torch.bfloat16
                 and self.o.dtype == torch.bfloat16 and norm.rms_fold() is not None and self.spec.hidden % 8 == 0
-                and self.q_dim % 8 == 0 and self.qkv.shape[0] < ops.WIDE_OUTPUT and self.qkv.data_ptr() % 16 == 0
+                and self.q_dim % 8 == 0 and self.qkv.data_ptr() % 16 == 0
                 and self.o.data_ptr() % 16 == 0)
 
     def forward_folded(self, batch, h: torch.Tensor, stats: RowStats, norm, cache, next_norm=None) -> RowStats:

@@ -69,14 +69,17 @@ class RowStats:
     prescaled_for: Optional[object] = None
 
 
+FOLD_ROWS = 64   # rows the buffers for ``RowStats`` hold; the kernels refuse more rows than their buffers have
+
+
 def fold_buffers(batch, which: int, width: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """One of the step's two pairs of buffers for ``RowStats`` (they alternate: a product reads one
     pair while the next product that changes the residual writes the other): statistics, float32
-    [8, capacity] with room for one partial sum per 16 columns of a residual ``width`` wide, and
-    prescaled rows, bfloat16 [8, width]."""
+    [64, capacity] with room for the partial sums a producing kernel leaves of a residual ``width``
+    wide (``ops.fold_capacity``), and prescaled rows, bfloat16 [64, width]."""
     capacity = max(8, (width + 15) // 16)
-    stats = batch.workspace(("row statistics", which & 1, capacity), 8 * capacity).view(8, capacity)
-    rows = batch.workspace(("prescaled rows", which & 1, width), 8 * width, torch.bfloat16).view(8, width)
+    stats = batch.workspace(("row statistics", which & 1, capacity), FOLD_ROWS * capacity).view(FOLD_ROWS, capacity)
+    rows = batch.workspace(("prescaled rows", which & 1, width), FOLD_ROWS * width, torch.bfloat16).view(FOLD_ROWS, width)
     return stats, rows
 
 

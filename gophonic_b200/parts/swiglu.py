@@ -52,13 +52,13 @@ class SwiGLU(FeedForward):
         self.rt.ops.gemm_add(self._activation(x), self.down, h)
 
     def folds_norm(self, rows: int, norm) -> bool:
-        """Single-token steps of up to eight rows in bfloat16, gate and up interleaved: the gate/up
+        """Steps of up to 64 rows in bfloat16, gate and up interleaved: the gate/up
         product applies the rows' norm factors from the residual's statistics, the down projection
         adds into the residual."""
         ops = self.rt.ops
-        return (rows <= ops.STAT_ROWS and self.interleaved and self.rt.act_dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16
+        return (rows <= ops.FOLD_ROWS and self.interleaved and self.rt.act_dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16
                 and norm.rms_fold() is not None and self.spec.hidden % 8 == 0 and self.spec.intermediate % 8 == 0
-                and self.gate_up.shape[0] < ops.WIDE_OUTPUT and self.gate_up.data_ptr() % 16 == 0 and self.down.data_ptr() % 16 == 0)
+                and self.gate_up.data_ptr() % 16 == 0 and self.down.data_ptr() % 16 == 0)
 
     def forward_folded(self, batch, h: torch.Tensor, stats: RowStats, norm, next_norm=None) -> RowStats:
         ops = self.rt.ops

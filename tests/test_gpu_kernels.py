@@ -115,8 +115,9 @@ def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
 
 
 # ---- few-row products with the norm and the residual add folded in ---------------------------
-@pytest.mark.parametrize("M", [1, 3, 8])
-@pytest.mark.parametrize("N,K,count", [(64, 64, 1), (1000, 96, 5), (6144, 4096, 256), (136, 2048, 128), (40, 520, 33)])
+# up to 8 rows the fragment-streaming kernel, 9 to 64 the tcgen05 decode kernel (alone and in clusters of K slices)
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K,count", [(64, 64, 1), (1000, 96, 5), (6144, 4096, 256), (136, 2048, 128), (40, 520, 33), (24576, 512, 7), (33024, 64, 3)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_that_applies_the_rows_norm_factors_from_statistics(ops, M, N, K, count, out_dtype):
     """out = rmsnorm(h) w^T where the rows arrive as bf16(h * norm weight) and each row's sum of
@@ -126,7 +127,7 @@ def test_gemm_that_applies_the_rows_norm_factors_from_statistics(ops, M, N, K, c
     h, nw = rnd(M, K, scale=3.0, seed=1), 1 + 0.1 * rnd(K, seed=2)
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=3)
     edges = torch.linspace(0, K, count + 1).round().long().tolist()
-    stats = torch.full((8, max(count, 8) + 3), float("nan"), device=DEV)
+    stats = torch.full((max(M, 8), max(count, 8) + 3), float("nan"), device=DEV)
     for c in range(count):
         stats[:M, c] = (h[:, edges[c]:edges[c + 1]].double() ** 2).sum(-1).float()
     x = (h * nw).to(torch.bfloat16)
@@ -139,20 +140,24 @@ def test_gemm_that_applies_the_rows_norm_factors_from_statistics(ops, M, N, K, c
     # against the norm itself: the rows were rounded to bfloat16 before instead of after the factor
     exact = (h.double() * rs * nw.double()) @ w.double().T
     close(out, exact, 1.2e-2)
-    if M > 1:   # a row's result does not depend on the other rows
+    if 1 < M <= 8:   # a row's result does not depend on the other rows
         one = torch.empty((1, N), dtype=out_dtype, device=DEV)
         ops.gemm_scaled(x[M - 1:].contiguous(), eps, stats[M - 1:].contiguous(), count, w, one)
         assert torch.equal(one[0], out[M - 1])
+    elif M > 8:      # nor on where among them it stands (another row count may mean another kernel)
+        back = torch.empty_like(out)
+        ops.gemm_scaled(x.flip(0).contiguous(), eps, stats[:M].flip(0).contiguous(), count, w, back)
+        assert torch.equal(back.flip(0), out)
 
 
-@pytest.mark.parametrize("M", [1, 5, 8])
-@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (12288 // 8, 512)])
+@pytest.mark.parametrize("M", [1, 5, 8, 12, 40, 64])
+@pytest.mark.parametrize("inter,K", [(8, 64), (136, 80), (12288 // 8, 512), (12288, 1024), (16512, 64)])
 def test_gemm_that_applies_the_rows_norm_factors_with_the_swiglu_epilogue(ops, M, inter, K):
     eps = 1e-6
     gate, up = rnd(inter, K, dtype=torch.bfloat16, scale=0.2, seed=1), rnd(inter, K, dtype=torch.bfloat16, scale=0.2, seed=2)
     w = torch.stack([gate.view(inter // 8, 8, K), up.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
     h, nw = rnd(M, K, scale=2.0, seed=3), 1 + 0.1 * rnd(K, seed=4)
-    stats = torch.zeros((8, 8), device=DEV)
+    stats = torch.zeros((max(M, 8), 8), device=DEV)
     stats[:M, 0] = (h.double() ** 2).sum(-1).float()
     x = (h * nw).to(torch.bfloat16)
     rs = 1.0 / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
@@ -162,36 +167,38 @@ def test_gemm_that_applies_the_rows_norm_factors_with_the_swiglu_epilogue(ops, M
     close(out, g / (1 + torch.exp(-g)) * u, 6e-3)
 
 
-@pytest.mark.parametrize("M", [1, 4, 8])
-@pytest.mark.parametrize("N,K", [(64, 64), (1000, 96), (4096, 12288), (4096, 4096), (40, 520)])
+@pytest.mark.parametrize("M", [1, 4, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(64, 64), (1000, 96), (4096, 12288), (4096, 4096), (40, 520), (5120, 1024), (19200, 128)])
 def test_gemm_that_adds_into_the_residual_and_prepares_the_next_norm(ops, M, N, K):
     """h += x w^T in the product's own epilogue: the bits of the product into a buffer and a float32
-    add; one partial sum of squares of the new residual per 16 columns; and the new rows times the
-    next norm's weight, rounded to bfloat16."""
+    add; partial sums of squares of the new residual, one per block of columns (16 wide up to 8
+    rows, 128 wide above); and the new rows times the next norm's weight, rounded to bfloat16."""
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
     h0, nw = rnd(M, N, seed=3), 1 + 0.1 * rnd(N, seed=4)
     prod = torch.empty((M, N), dtype=torch.float32, device=DEV)
-    ops.gemm(x, w, prod, algo="skinny")
+    ops.gemm(x, w, prod, algo="skinny" if M <= 8 else "tc5_decode")
     h = h0.clone()
-    count = (N + 15) // 16
-    stats = torch.full((8, count + 2), float("nan"), device=DEV)
+    room = ops.fold_capacity(N)
+    stats = torch.full((max(M, 8), room + 2), float("nan"), device=DEV)
     nxt = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     assert ops.gemm_residual_accepts(x, w, h)
-    assert ops.gemm_residual(x, w, h, stats, nw, nxt) == count
+    count = ops.gemm_residual(x, w, h, stats, nw, nxt)
+    block = 16 if M <= 8 else 128
+    assert count == (N + block - 1) // block
     assert torch.equal(h, h0 + prod)
     close(h, h0.double() + x.double() @ w.double().T, 2e-5)
     assert torch.equal(nxt, (h * nw).to(torch.bfloat16))
-    pad = torch.zeros((M, count * 16), dtype=torch.float64, device=DEV)
+    pad = torch.zeros((M, count * block), dtype=torch.float64, device=DEV)
     pad[:, :N] = h.double()
-    want = (pad ** 2).view(M, count, 16).sum(-1)
+    want = (pad ** 2).view(M, count, block).sum(-1)
     assert (stats[:M, :count].double() - want).abs().max() <= 1e-5 * want.abs().max()
     assert torch.isnan(stats[M:]).all() and torch.isnan(stats[:, count:]).all()      # nothing else is written
     # without a next norm only the residual and the statistics are written
-    h2, stats2 = h0.clone(), torch.zeros((8, count), device=DEV)
-    ops.gemm_residual(x, w, h2, stats2)
-    assert torch.equal(h2, h) and torch.equal(stats2[:M], stats[:M, :count])
+    h2, stats2 = h0.clone(), torch.zeros((max(M, 8), room), device=DEV)
+    assert ops.gemm_residual(x, w, h2, stats2) == count
+    assert torch.equal(h2, h) and torch.equal(stats2[:M, :count], stats[:M, :count])
     with pytest.raises(ops.KernelError):
-        ops.gemm_residual(rnd(9, K, dtype=torch.bfloat16), w, torch.zeros((9, N), device=DEV), torch.zeros((9, count), device=DEV))
+        ops.gemm_residual(rnd(65, K, dtype=torch.bfloat16), w, torch.zeros((65, N), device=DEV), torch.zeros((65, room), device=DEV))
     with pytest.raises(ops.KernelError, match="without a tensor"):
         ops.gemm_residual(x, w, h2, stats2, nw, None)
 
