@@ -41,15 +41,20 @@ GB_API int gb_dispatch_constant(int which) {
 }
 
 // The tensor-core kernel for aligned bfloat16 operands of these sizes (measured on the four products
-// of an 8B layer, 1 to 2048 rows).
+// of a layer at 1.7B, 8B and 32B sizes, 1 to 2048 rows).
 GB_API int gb_gemm_algo(int M, int N, int K, int sms) {
+    (void)K;
     if (M <= SKINNY_MAX_ROWS && N < WIDE_OUTPUT) return GB_ALGO_SKINNY;  // weights streamed straight into mma.sync fragments
     if (M <= 64) return GB_ALGO_TC5_DECODE;                               // tcgen05, weights on the M side, K slices across a cluster
-    if (M <= TC5_DECODE_MAX_ROWS / 2)
-        // up to 128 rows the step is still bound by reading the weights: the decode kernel gives every
-        // SM a share of them, the tiled kernel only where the output is wide enough for that
-        return (N + 127) / 128 < sms ? GB_ALGO_TC5_DECODE : GB_ALGO_TC5;
-    if (M <= TC5_DECODE_MAX_ROWS && (N + 255) / 256 <= 16 && K >= 8192) return GB_ALGO_TC5_DECODE;  // a narrow output with a long K
+    // Up to 256 rows a narrow output is still bound by reading its weights, and the decode kernel gives
+    // every SM a share of them by cutting K; its CTAs all read the activations, though, so a wide output
+    // is better off on the tiled kernels.  Tiles of 128 output columns against the SM count: at 65 to
+    // 128 rows the decode kernel won at 80 tiles (10240 x 5120: 36 against 45 us) and lost at 96
+    // (12288 x 2048: 28 against 18 us); at 129 to 256 rows it won at 40 (5120 x 8192: 44 against 48 us;
+    // 4096 x 4096: 19 against 26 us), tied at 48 and lost at 80 (75 against 38 us).
+    const int tiles = (N + 127) / 128;
+    if (M <= TC5_DECODE_MAX_ROWS / 2) return 5 * tiles <= 3 * sms ? GB_ALGO_TC5_DECODE : GB_ALGO_TC5;
+    if (M <= TC5_DECODE_MAX_ROWS && 10 * tiles <= 3 * sms) return GB_ALGO_TC5_DECODE;
     if (M >= TC5_PAIR_MIN_ROWS) return GB_ALGO_TC5_PAIR;                  // tcgen05 on pairs of SMs, 256 x 256 tiles
     return GB_ALGO_TC5;                                                   // tcgen05, 128 x 256 tiles
 }

@@ -362,12 +362,15 @@ template <typename TC>
 int dispatch(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldy, int epi, int splits,
              const DecodeFold& fold, cudaStream_t stream) {
     if (M <= 16) return launch<TC, 16, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, fold, stream);
-    if (M <= 32) return launch<TC, 32, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, fold, stream);
     // More tiles than SMs but fewer than two to an SM (the gate/up product of an 8B layer: 192 tiles on
     // 148 SMs): some SMs would stream two tiles while most stream one.  Such a product runs in two K
     // slices with three stages, so that three CTAs fit an SM and every SM gets two or three of the
     // smaller pieces (64 rows: 50.7 -> 43.3 us; 33 rows: 43.5 -> 38.4 us).
     const bool uneven = splits == 2 && ceil_div(N, BMW) > UNEVEN_TILES;
+    if (M <= 32) {
+        if (uneven) return launch<TC, 32, 3>(X, W, Y, M, N, K, ldx, ldy, epi, splits, fold, stream);
+        return launch<TC, 32, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, fold, stream);
+    }
     if (M <= 64) {
         if (uneven) return launch<TC, 64, 3>(X, W, Y, M, N, K, ldx, ldy, epi, splits, fold, stream);
         return launch<TC, 64, 4>(X, W, Y, M, N, K, ldx, ldy, epi, splits, fold, stream);
@@ -391,7 +394,7 @@ GB_API int gb_gemm_tc5_decode_splits(int M, int N, int K, int sms) {
     if (sms <= 0) sms = 1;
     if (M > 16) {
         int per_sm = M > 128 ? 1 : 2;  // CTAs that fit on an SM with the operand stages of this many rows
-        if (M > 32 && M <= 64 && tiles > UNEVEN_TILES && tiles > sms && tiles < 2 * sms) per_sm = 3;  // see dispatch(): three stages
+        if (M <= 64 && tiles > UNEVEN_TILES && tiles > sms && tiles < 2 * sms) per_sm = 3;  // see dispatch(): three stages
         int want = (per_sm * sms) / (tiles > 0 ? tiles : 1);
         if (want > KB / 8) want = KB / 8;
         int s = 1;
