@@ -367,9 +367,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
     """out = a @ w^T, choosing the kernel by operand types and sizes.  Returns the kernel's name.
 
     bfloat16 activations with bfloat16 weights go to the tensor-core kernels (``gemm_algo``): up to
-    8 rows the fragment-streaming kernel, up to 128 (256 for narrow outputs with a long K) the
-    tcgen05 decode kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs
-    two SMs on a tile.  Everything else,
+    8 rows the fragment-streaming kernel, up to 64 rows (128 or 256 for narrow outputs) the tcgen05
+    decode kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs two SMs
+    on a tile.  Everything else,
     and operands whose rows are not 16-byte aligned, goes to the fp32 CUDA-core kernel.  float32
     operands never touch a tensor core.
     """

@@ -136,7 +136,9 @@ def test_a_batch_of_unequal_prompts_whose_shorter_requests_end_earlier(wide, dty
     entry = wide(dtype)
     eng, pcfg, _, _, columns = entry
     rng = np.random.default_rng(29)
-    for plan in ([(150, 4), (40, 2), (70, 6)], [(9, 3), (300, 1)]):     # the second batch uses the slots and pages again
+    # the second batch uses the slots and pages again; the third decodes ten sequences together, where
+    # the products of 9 to 64 rows carry the norms at these widths (32 tiles of 128 columns, 8 K slices)
+    for plan in ([(150, 4), (40, 2), (70, 6)], [(9, 3), (300, 1)], [(2 + (7 * i) % 23, 2) for i in range(10)]):
         toks = [rng.integers(0, pcfg["vocab_size"], size=p + d).tolist() for p, d in plan]
         refs = [reference(entry, t) for t in toks]
         slots = [eng.new_sequence() for _ in plan]
