@@ -316,21 +316,22 @@ def probe(name, **opts):
             state["i"] += 1
         work = N * K * 2.0
         unit = "GB/s"
-    elif name in ("gemm_scaled_b8", "gemm_residual_b8"):
-        # the two few-row products of a decode step that carry the residual's row-wise work: gate/up
-        # with the rows' norm factors and SwiGLU in its epilogue, and the down projection that adds
-        # into the residual and leaves the row statistics and the next norm's rows
-        M = 8
-        N, K = (24576, 4096) if name == "gemm_scaled_b8" else (4096, 12288)
+    elif name in ("gemm_scaled_b8", "gemm_residual_b8", "gemm_scaled_b64", "gemm_residual_b64"):
+        # the two products of a decode step that carry the residual's row-wise work: gate/up with the
+        # rows' norm factors and SwiGLU in its epilogue, and the down projection that adds into the
+        # residual and leaves the row statistics and the next norm's rows (8 rows: the fragment-streaming
+        # kernel; 64 rows: the tcgen05 decode kernel)
+        M = 8 if name.endswith("b8") else 64
+        N, K = (24576, 4096) if name.startswith("gemm_scaled") else (4096, 12288)
         ws = [rnd(N, K, scale=0.05) for _ in range(max(3, int(6e8 / (2.0 * N * K))))]
         x = rnd(M, K)
-        stats = torch.ones((8, max(K, N) // 16), device=dev)
+        stats = torch.ones((M, max(K, N) // 16), device=dev)
         state = {"i": 0}
-        if name == "gemm_scaled_b8":
+        if name.startswith("gemm_scaled"):
             out = torch.empty((M, N // 2), dtype=bf, device=dev)
 
             def fn():
-                ops.gemm_scaled(x, 1e-6, stats, K // 16, ws[state["i"] % len(ws)], out, swiglu=True)
+                ops.gemm_scaled(x, 1e-6, stats, K // (16 if M <= 8 else 128), ws[state["i"] % len(ws)], out, swiglu=True)
                 state["i"] += 1
         else:
             h = torch.zeros((M, N), device=dev)
@@ -414,7 +415,7 @@ def probe(name, **opts):
 
 
 KERNEL_PROBES = ("gemm_prefill", "gemm_prefill_swiglu", "attn_prefill", "gemm_decode_b8", "gemm_scaled_b8", "gemm_residual_b8",
-                 "gemm_decode_b64", "gemm_down_b128", "attn_decode_b8", "attn_decode_b64")
+                 "gemm_decode_b64", "gemm_scaled_b64", "gemm_residual_b64", "gemm_down_b128", "attn_decode_b8", "attn_decode_b64")
 
 
 def profile():
