@@ -210,13 +210,91 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
 // ------------------------------------------------------------------------------------------
 constexpr int DSTAGES = 3;
 
+// What the single-token kernel needs to do the work of the row-wise q/k norm + rotation + cache write
+// kernel (elementwise.cu) itself: the queries then arrive as the q/k/v product left them, and the
+// token's own key and value are not in the cache yet.
+struct RopeFuse {
+    int on;
+    const float* q_w;   // per-head norm weights, or null
+    const float* k_w;
+    float eps;
+    const float* cos_t;  // [table_positions][rot / 2]
+    const float* sin_t;
+    int rot;
+    int table_positions;
+    int write_kv;        // store the token's key and value in the cache planes
+    int consecutive;     // head_dim 128 rotated in full: the lane layout and order of sums of the row-wise kernel's fast path
+};
+
+// One head row of HD bfloat16 in shared memory, normed (if w) and rotated in place by one warp, with
+// the arithmetic and the order of sums of the row-wise kernel for the same geometry, so that a key
+// written by either is the same bits.  y: HD floats of scratch for this warp.
+template <int HD>
+__device__ __forceinline__ void norm_rope_row(bf16* x, float* y, const float* __restrict__ w, float eps, const float* __restrict__ c,
+                                              const float* __restrict__ s, int rot, int lane, bool consecutive) {
+    if (HD == 128 && consecutive) {
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(x + lane * 4), hi = *reinterpret_cast<const __nv_bfloat162*>(x + lane * 4 + 2);
+        float v[4] = {__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi)};
+        if (w) {
+            const float4 ww = *reinterpret_cast<const float4*>(w + lane * 4);
+            float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+            const float inv = 1.0f / sqrtf(ss / 128.f + eps);
+            v[0] = v[0] * inv * ww.x;
+            v[1] = v[1] * inv * ww.y;
+            v[2] = v[2] * inv * ww.z;
+            v[3] = v[3] * inv * ww.w;
+        }
+        const int ci = (lane & 15) * 4;
+        const float4 c4 = *reinterpret_cast<const float4*>(c + ci), s4 = *reinterpret_cast<const float4*>(s + ci);
+        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float partner = __shfl_xor_sync(0xffffffffu, v[e], 16);
+            o[e] = lane < 16 ? v[e] * cs[e] - partner * sv[e] : v[e] * cs[e] + partner * sv[e];
+        }
+        *reinterpret_cast<__nv_bfloat162*>(x + lane * 4) = __floats2bfloat162_rn(o[0], o[1]);
+        *reinterpret_cast<__nv_bfloat162*>(x + lane * 4 + 2) = __floats2bfloat162_rn(o[2], o[3]);
+        return;
+    }
+    float ss = 0.f;
+    for (int i = lane; i < HD; i += 32) {
+        float v = __bfloat162float(x[i]);
+        y[i] = v;
+        ss += v * v;
+    }
+    float inv = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)HD + eps);
+    }
+    __syncwarp();
+    if (w)
+        for (int i = lane; i < HD; i += 32) y[i] = y[i] * inv * w[i];
+    __syncwarp();
+    const int half = rot / 2;
+    for (int i = lane; i < HD; i += 32) {
+        float v;
+        if (i < half)
+            v = y[i] * c[i] - y[i + half] * s[i];
+        else if (i < rot)
+            v = y[i] * c[i - half] + y[i - half] * s[i - half];
+        else
+            v = y[i];
+        x[i] = __float2bfloat16_rn(v);
+    }
+    __syncwarp();
+}
+
 template <int HD, bool QREG>
-__global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, RopeFuse f) {
     constexpr int SD = HD + 8, KS = HD / 16, NF = HD / 8;
     constexpr int STAGE = 2 * 64 * SD;  // elements: keys then values
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [16][SD]
     bf16* KV = Qs + 16 * SD;                          // [DSTAGES][2][64][SD]
+    float* Ys = reinterpret_cast<float*>(KV + DSTAGES * STAGE);  // [4 warps][HD]: scratch of norm_rope_row
+    bf16* fresh = reinterpret_cast<bf16*>(Ys + 4 * HD);          // [2][HD]: the token's own key and value
 
     pdl_wait();
     pdl_trigger();  // the product that follows may start fetching its weights
@@ -243,6 +321,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
             bool ok = row < nh;
             cp_async16(Qs + row * SD + c * 8, ok ? qsrc + (int64_t)row * HD + c * 8 : qsrc, ok ? 16 : 0);
         }
+        if (f.on) cp_async_commit();  // a group of their own: they are needed before the first keys are
     }
     int lo_pos = 0;
     if (p.window > 0) {
@@ -269,6 +348,45 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
         cp_async_commit();
     }
 
+    // The CTA whose keys end with the token's own page has that key and value from the q/k/v product's
+    // row, not from the cache: the last tile is patched in shared memory, and one CTA per kv head also
+    // stores them in the cache for the steps to come.
+    const bool owns_last = f.on && n > 0 && my_hi == t_hi;
+    if (f.on && n > 0) {
+        const int half = f.rot / 2;
+        // rows whose position lies beyond the table are refused on the host
+        const int tpos = (half == 0 || gb_check(pos, f.table_positions, GB_CHECK_ROPE_POSITION)) ? pos : 0;
+        const float* cs = f.cos_t + (int64_t)tpos * half;
+        const float* sn = f.sin_t + (int64_t)tpos * half;
+        const bf16* row = (const bf16*)p.q + (int64_t)q_row * p.q_row_stride;
+        if (owns_last) {
+            const bf16* ksrc = row + (int64_t)(p.heads + kvh) * HD;
+            const bf16* vsrc = row + (int64_t)(p.heads + p.kv_heads + kvh) * HD;
+            for (int i = tid; i < 2 * HD; i += 128) fresh[i] = i < HD ? ksrc[i] : vsrc[i - HD];
+        }
+        cp_async_wait<DSTAGES - 1>();  // the queries have landed; the first tiles may still be on their way
+        __syncthreads();
+        for (int task = warp; task < nh + (owns_last ? 1 : 0); task += 4) {
+            if (task < nh)
+                norm_rope_row<HD>(Qs + task * SD, Ys + warp * HD, f.q_w, f.eps, cs, sn, f.rot, lane, f.consecutive != 0);
+            else
+                norm_rope_row<HD>(fresh, Ys + warp * HD, f.k_w, f.eps, cs, sn, f.rot, lane, f.consecutive != 0);
+        }
+        __syncthreads();
+        if (owns_last && chunk == 0 && f.write_kv) {
+            const int64_t page = page_of(bt, pos, p.bt_stride, p.pages);
+            const int64_t at = ((page * p.kv_heads + kvh) * 64 + (pos & 63)) * (int64_t)HD;
+            bf16* kdst = (bf16*)p.k_plane + at;
+            bf16* vdst = (bf16*)p.v_plane + at;
+            for (int i = tid; i < 2 * HD; i += 128) {
+                if (i < HD)
+                    kdst[i] = fresh[i];
+                else
+                    vdst[i - HD] = fresh[i];
+            }
+        }
+    }
+
     const float sc = p.scale * LOG2E;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float o[NF][4];
@@ -287,6 +405,17 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p) {
 #pragma unroll
             for (int ks = 0; ks < KS; ks++)
                 ldmatrix_x4(qf[QREG ? ks : 0], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks * 16 + (lane >> 4) * 8);
+        }
+        if (owns_last && i == n - 1) {
+            // the token's own key and value over whatever the cache held at its place
+            bf16* krow = KV + (i % DSTAGES) * STAGE + (pos & 63) * SD;
+            for (int idx = tid; idx < 2 * HD; idx += 128) {
+                if (idx < HD)
+                    krow[idx] = fresh[idx];
+                else
+                    krow[64 * SD + idx - HD] = fresh[idx];
+            }
+            __syncthreads();
         }
         const bf16* kt = KV + (i % DSTAGES) * STAGE;
         const bf16* vt = kt + 64 * SD;
@@ -429,10 +558,10 @@ int launch_prefill(const AttnParams& p, cudaStream_t stream) {
 }
 
 template <int HD>
-int launch_decode(const AttnParams& p, cudaStream_t stream) {
+int launch_decode(const AttnParams& p, const RopeFuse& f, cudaStream_t stream) {
     constexpr bool QREG = HD <= 128;
     constexpr int SD = HD + 8;
-    int smem = (16 * SD + DSTAGES * 2 * 64 * SD) * 2;
+    int smem = (16 * SD + DSTAGES * 2 * 64 * SD) * 2 + 4 * HD * 4 + 2 * HD * 2;
     const int merge = (128 + 64 * HD) * 4 + 16 * SD * 2;
     if (merge > smem) smem = merge;
     static bool configured = false;
@@ -450,9 +579,9 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     // is alone (one split, many CTAs) and loses when its CTAs and those of the merge behind it sit
     // waiting beside the kernels ahead, so only the single-split form is a dependent launch.
     if (p.num_splits == 1)
-        launch_pdl(attn_decode_mma_kernel<HD, QREG>, grid, dim3(128), (size_t)smem, stream, p);
+        launch_pdl(attn_decode_mma_kernel<HD, QREG>, grid, dim3(128), (size_t)smem, stream, p, f);
     else
-        attn_decode_mma_kernel<HD, QREG><<<grid, 128, smem, stream>>>(p);
+        attn_decode_mma_kernel<HD, QREG><<<grid, 128, smem, stream>>>(p, f);
     GB_CHECK_LAUNCH("attention_decode_mma");
     if (p.num_splits > 1)
         return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, p.d,
@@ -472,17 +601,17 @@ int check(const AttnParams& p, const char* who) {
 
 }  // namespace
 
-#define GB_DISPATCH_HD(fn)                                 \
+#define GB_DISPATCH_HD(fn, ...)                            \
     switch (p.d) {                                         \
-        case 16: return fn<16>(p, stream);                 \
-        case 32: return fn<32>(p, stream);                 \
-        case 48: return fn<48>(p, stream);                 \
-        case 64: return fn<64>(p, stream);                 \
-        case 80: return fn<80>(p, stream);                 \
-        case 96: return fn<96>(p, stream);                 \
-        case 112: return fn<112>(p, stream);               \
-        case 128: return fn<128>(p, stream);               \
-        case 256: return fn<256>(p, stream);               \
+        case 16: return fn<16>(p, ##__VA_ARGS__, stream);  \
+        case 32: return fn<32>(p, ##__VA_ARGS__, stream);  \
+        case 48: return fn<48>(p, ##__VA_ARGS__, stream);  \
+        case 64: return fn<64>(p, ##__VA_ARGS__, stream);  \
+        case 80: return fn<80>(p, ##__VA_ARGS__, stream);  \
+        case 96: return fn<96>(p, ##__VA_ARGS__, stream);  \
+        case 112: return fn<112>(p, ##__VA_ARGS__, stream); \
+        case 128: return fn<128>(p, ##__VA_ARGS__, stream); \
+        case 256: return fn<256>(p, ##__VA_ARGS__, stream); \
     }
 
 GB_API int gb_attention_prefill_mma(const AttnParams* pp, cudaStream_t stream) {
@@ -501,8 +630,52 @@ GB_API int gb_attention_decode_mma(const AttnParams* pp, cudaStream_t stream) {
     if (p.max_q_len != 1) GB_REFUSE("attention_decode_mma: rows of up to %d tokens; this kernel takes single tokens", p.max_q_len);
     if (p.num_splits < 1) GB_REFUSE("attention_decode_mma: %d key splits", p.num_splits);
     if (p.num_splits > 1 && !p.scratch) GB_REFUSE("attention_decode_mma: %d key splits without scratch memory", p.num_splits);
-    GB_DISPATCH_HD(launch_decode)
+    const RopeFuse off = {};
+    GB_DISPATCH_HD(launch_decode, off)
     GB_REFUSE("attention_decode_mma: head_dim %d", p.d);
+}
+
+// Whether the single-token kernel can do the q/k norm, the rotation and the cache write of these rows
+// itself (bfloat16, a head size it takes, one row a sequence).
+GB_API int gb_attention_decode_rope_accepts(int dtype, int d, int rot, int max_q_len) {
+    return dtype == GB_BF16 && max_q_len == 1 && !(d & 15) && (d <= 128 || d == 256) && rot >= 0 && rot <= d && !(rot & 1);
+}
+
+// Single-token attention on rows as the q/k/v product left them: `a` describes the attention call
+// (a->q the rows of the fused q|k|v buffer), `r` what gb_qk_norm_rope_kv_write would have been given
+// for the same rows.  Each CTA norms and rotates the queries of its heads; the CTA that reads a
+// sequence's last page takes the token's own key and value from the row, and one CTA per kv head
+// stores them in the cache.  The same bits as the two kernels one after the other.
+GB_API int gb_attention_decode_mma_rope(const AttnParams* pp, const QkRopeParams* rp, cudaStream_t stream) {
+    AttnParams p = *pp;
+    const QkRopeParams& r = *rp;
+    if (p.nseq <= 0) return 0;
+    const char* who = "attention_decode_mma_rope";
+    if (int rc = check(p, who)) return rc;
+    if (p.max_q_len != 1) GB_REFUSE("%s: rows of up to %d tokens; this kernel takes single tokens", who, p.max_q_len);
+    if (p.num_splits < 1) GB_REFUSE("%s: %d key splits", who, p.num_splits);
+    if (p.num_splits > 1 && !p.scratch) GB_REFUSE("%s: %d key splits without scratch memory", who, p.num_splits);
+    if (r.qkv != p.q || r.row_stride != p.q_row_stride || r.heads != p.heads || r.kv_heads != p.kv_heads || r.d != p.d ||
+        r.rows != p.nseq || r.block_table != p.block_table || r.bt_stride != p.bt_stride)
+        GB_REFUSE("%s: the two descriptions are not of the same rows", who);
+    if (r.write_kv && (r.k_plane != p.k_plane || r.v_plane != p.v_plane)) GB_REFUSE("%s: keys would be written to another plane than is read", who);
+    if (!gb_attention_decode_rope_accepts(GB_BF16, p.d, r.rot, p.max_q_len)) GB_REFUSE("%s: head_dim %d, rotary width %d", who, p.d, r.rot);
+    if (r.rot > 0 && (!r.cos_t || !r.sin_t)) GB_REFUSE("%s: rotary width %d without an angle table", who, r.rot);
+    RopeFuse f = {};
+    f.on = 1;
+    f.q_w = r.q_w;
+    f.k_w = r.k_w;
+    f.eps = r.eps;
+    f.cos_t = r.cos_t;
+    f.sin_t = r.sin_t;
+    f.rot = r.rot;
+    f.table_positions = r.table_positions;
+    f.write_kv = r.write_kv;
+    // the row-wise kernel's own condition for its fast path (elementwise.cu)
+    f.consecutive = p.d == 128 && r.rot == 128 && !(r.row_stride & 3) && !((uintptr_t)r.qkv & 7) &&
+                    !(((uintptr_t)r.q_w | (uintptr_t)r.k_w | (uintptr_t)r.cos_t | (uintptr_t)r.sin_t) & 15) && (r.q_w != nullptr) == (r.k_w != nullptr);
+    GB_DISPATCH_HD(launch_decode, f)
+    GB_REFUSE("%s: head_dim %d", who, p.d);
 }
 
 // the checked build's record of the first index this file's kernels found out of bounds

@@ -495,13 +495,12 @@ class _QkRopeParams(Structure):
     ]
 
 
-def qk_norm_rope_kv_write(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
-                          q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
-                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
-                          row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
-                          block_table: torch.Tensor,
-                          k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool) -> None:
-    """Per-head RMSNorm of q and k, rotary embedding of both, q in place, k and v into the cache."""
+def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                 q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                 row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
+                 block_table: torch.Tensor,
+                 k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool) -> "_QkRopeParams":
     _need(qkv, "qkv", dim=2)
     rows = qkv.shape[0]
     if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
@@ -534,6 +533,14 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim
                       0 if k_plane is None else k_plane.data_ptr(), 0 if v_plane is None else v_plane.data_ptr(),
                       1 if write_kv else 0, rows, heads, kv_heads, head_dim,
                       0 if k_plane is None else k_plane.shape[0], block_table.shape[0])
+    return p
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, *args) -> None:
+    """Per-head RMSNorm of q and k, rotary embedding of both, q in place, k and v into the cache:
+    (qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, cos, sin, rotary_dim, row_pos, row_seq,
+    seq_slot, block_table, k_plane, v_plane, write_kv)."""
+    p = _rope_params(qkv, *args)
     _check(_lib.gb_qk_norm_rope_kv_write(byref(p), _code(qkv.dtype), _stream()))
 
 
@@ -552,13 +559,11 @@ def attention_scratch_floats(nseq: int, heads: int, head_dim: int, num_splits: i
     return nseq * heads * num_splits * (head_dim + 2)
 
 
-def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
-              block_table: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
-              seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
-              heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
-              num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto") -> str:
-    """Causal GQA over the paged cache.  q is a [rows, >= heads*head_dim] view (row stride free),
-    out is [rows, heads*head_dim].  Returns the kernel's name."""
+def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                 block_table: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+                 seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
+                 heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
+                 num_splits: int, scratch: Optional[torch.Tensor]) -> "_AttnParams":
     _need(q, "attention q", dim=2, contiguous=False)
     _need(out, "attention out", q.dtype, 2, contiguous=False)
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] < heads * head_dim or out.shape[1] < heads * head_dim:
@@ -584,6 +589,18 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr(),
                     k_plane.shape[0], block_table.shape[0])
+    return p
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+              block_table: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+              seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
+              heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
+              num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto") -> str:
+    """Causal GQA over the paged cache.  q is a [rows, >= heads*head_dim] view (row stride free),
+    out is [rows, heads*head_dim].  Returns the kernel's name."""
+    p = _attn_params(q, out, k_plane, v_plane, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, nseq, max_q_len,
+                     heads, kv_heads, head_dim, scale, window, num_splits, scratch)
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
         algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
@@ -598,6 +615,22 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
     else:
         raise KernelError(f"attention: unknown algorithm '{algo}'")
     return algo
+
+
+def attention_decode_rope_accepts(dtype: torch.dtype, head_dim: int, rotary_dim: int, max_q_len: int) -> bool:
+    """Whether ``attention_decode_rope`` takes rows of this kind (bfloat16, one row a sequence, a head
+    size the tensor-core single-token kernel takes)."""
+    return dtype in (torch.float32, torch.bfloat16) and bool(_lib.gb_attention_decode_rope_accepts(_code(dtype), c_int(head_dim), c_int(rotary_dim), c_int(max_q_len)))
+
+
+def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, rope_args: tuple, attn_args: tuple) -> None:
+    """``qk_norm_rope_kv_write(qkv, *rope_args)`` and ``attention(qkv[:, :heads * head_dim], out,
+    *attn_args)`` for single-token rows in one kernel (plus the merge of key splits): the attention
+    kernel norms and rotates its queries itself, takes the token's own key and value from the row and
+    stores them in the cache.  The same bits as the two calls."""
+    r = _rope_params(qkv, *rope_args)
+    a = _attn_params(qkv[:, :r.heads * r.d], out, *attn_args)
+    _check(_lib.gb_attention_decode_mma_rope(byref(a), byref(r), _stream()), 2 if a.num_splits > 1 else 1)
 
 
 # ---- a whole pre-norm layer from one call ---------------------------------------------------

@@ -172,13 +172,16 @@ class Attention(Mixer):
         if cache.k.dtype != x.dtype:
             raise ValueError(f"attention: cache holds {cache.k.dtype}, activations are {x.dtype}")
         cos, sin, rot = self.position.kernel_args()
-        ops.qk_norm_rope_kv_write(qkv, s.heads, s.kv_heads, s.head_dim, self.q_norm, self.k_norm, self.eps,
-                                  cos, sin, rot, batch.row_pos, batch.row_seq, batch.seq_slot,
-                                  cache.block_table, cache.k, cache.v, cache.writable)
+        rope_args = (s.heads, s.kv_heads, s.head_dim, self.q_norm, self.k_norm, self.eps, cos, sin, rot, batch.row_pos,
+                     batch.row_seq, batch.seq_slot, cache.block_table, cache.k, cache.v, cache.writable)
         ctx = torch.empty((rows, self.q_dim), dtype=x.dtype, device=x.device)
         splits, scratch = self.key_splits(batch)
-        ops.attention(qkv[:, :self.q_dim], ctx, cache.k, cache.v, cache.block_table,
-                      batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len, batch.nseq,
-                      batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),
-                      splits, scratch)
+        attn_args = (cache.k, cache.v, cache.block_table, batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len,
+                     batch.nseq, batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window), splits, scratch)
+        if ops.attention_decode_rope_accepts(x.dtype, s.head_dim, rot, batch.max_q_len):
+            # single tokens: the attention kernel norms and rotates its queries and places the token's key and value itself
+            ops.attention_decode_rope(qkv, ctx, rope_args, attn_args)
+        else:
+            ops.qk_norm_rope_kv_write(qkv, *rope_args)
+            ops.attention(qkv[:, :self.q_dim], ctx, *attn_args)
         return ctx

@@ -540,6 +540,47 @@ def test_attention_single_tokens(ops, dtype, algo, heads, kvh, d, splits):
         assert used == "decode_mma"
 
 
+@pytest.mark.parametrize("heads,kvh,d,rot", [(4, 2, 16, 16), (5, 1, 48, 32), (32, 8, 128, 128), (8, 2, 128, 64), (20, 1, 32, 0), (2, 2, 256, 256),
+                                              (40, 2, 64, 64), (6, 3, 112, 112)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("normed", [True, False])
+def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, heads, kvh, d, rot, splits, normed):
+    """One kernel instead of two: the queries are normed and rotated by the attention kernel, the
+    token's own key and value come from the q/k/v row and are stored in the cache.  The output and
+    the cache afterwards are the bits the two kernels one after the other give."""
+    kv_lens = [1, 64, 65, 700, 333, 128]
+    nseq = len(kv_lens)
+    assert ops.attention_decode_rope_accepts(torch.bfloat16, d, rot, 1)
+    max_pages = (max(kv_lens) + 63) // 64
+    n_pages = nseq * max_pages + 2
+    table = torch.randperm(n_pages - 1, generator=torch.Generator().manual_seed(5))[:nseq * max_pages].to(torch.int32).reshape(nseq, max_pages).to(DEV)
+    k0, v0 = paged(n_pages, kvh, d, torch.bfloat16, 11)
+    qkv0 = rnd(nseq, (heads + 2 * kvh) * d, dtype=torch.bfloat16, seed=12)
+    qw, kw = (1 + 0.1 * rnd(d, seed=13), 1 + 0.1 * rnd(d, seed=14)) if normed else (None, None)
+    cos = torch.cos(rnd(800, max(rot // 2, 1), seed=15)) if rot else None
+    sin = torch.sin(rnd(800, max(rot // 2, 1), seed=15)) if rot else None
+    mk = lambda x: torch.tensor(list(x), dtype=torch.int32, device=DEV)
+    pos, seqs, slots = mk([n - 1 for n in kv_lens]), mk(range(nseq)), mk(range(nseq))
+    scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, d, splits), dtype=torch.float32, device=DEV) if splits > 1 else None
+    results = []
+    for fused in (False, True):
+        qkv, k, v = qkv0.clone(), k0.clone(), v0.clone()
+        out = torch.full((nseq, heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        rope_args = (heads, kvh, d, qw, kw, 1e-6, cos, sin, rot, pos, seqs, slots, table, k, v, True)
+        attn_args = (k, v, table, slots, mk(range(nseq)), mk([1] * nseq), mk(kv_lens), nseq, 1, heads, kvh, d, d ** -0.5, 0, splits, scratch)
+        if fused:
+            ops.attention_decode_rope(qkv, out, rope_args, attn_args)
+            assert torch.equal(qkv, qkv0)          # the rows stay as the product left them
+        else:
+            ops.qk_norm_rope_kv_write(qkv, *rope_args)
+            ops.attention(qkv[:, :heads * d], out, *attn_args, algo="decode_mma")
+        results.append((out, k, v))
+    (out_a, k_a, v_a), (out_b, k_b, v_b) = results
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    assert torch.equal(out_a, out_b)
+    assert not torch.equal(k_a, k0)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kvh,d", [(8, 2, 24), (3, 1, 40), (2, 2, 6)])
 def test_attention_head_sizes_that_are_no_multiple_of_16(ops, dtype, heads, kvh, d):
