@@ -92,4 +92,6 @@ GB_API int gb_gemm_tc5_decode(const void* X, const void* W, void* Y, int c_dtype
 GB_API int gb_attention_simt(const AttnParams* p, int dtype, cudaStream_t stream);
 GB_API int gb_attention_decode_mma(const AttnParams* p, cudaStream_t stream);
 GB_API int gb_attention_prefill_mma(const AttnParams* p, cudaStream_t stream);
+GB_API int gb_attention_decode_rope_accepts(int dtype, int d, int rot, int max_q_len);
+GB_API int gb_attention_decode_mma_rope(const AttnParams* p, const QkRopeParams* r, cudaStream_t stream);
 GB_API int gb_attention_prefill_tc5(const AttnParams* p, int rows, int pages, cudaStream_t stream);

@@ -296,8 +296,10 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
     float* Ys = reinterpret_cast<float*>(KV + DSTAGES * STAGE);  // [4 warps][HD]: scratch of norm_rope_row
     bf16* fresh = reinterpret_cast<bf16*>(Ys + 4 * HD);          // [2][HD]: the token's own key and value
 
-    pdl_wait();
-    pdl_trigger();  // the product that follows may start fetching its weights
+    // Ahead of the dependency wait: the step's metadata and the pages of earlier steps, none of which
+    // the kernel before this one writes (the step's metadata is uploaded before its first kernel,
+    // and every kernel waits for its predecessor before it lets its successor start).  With
+    // `f.on` that includes the page the token's own key will go to: only this kernel writes there.
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int G = p.heads / p.kv_heads;
     const int GC = G < 16 ? G : 16;
@@ -312,17 +314,6 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
     const bf16* vbase = (const bf16*)p.v_plane;
     const int h0 = kvh * G + chunk * GC;            // first head of this CTA
     const int nh = (G - chunk * GC) < GC ? (G - chunk * GC) : GC;  // heads of this CTA
-
-    {
-        constexpr int CH = HD / 8;
-        const bf16* qsrc = (const bf16*)p.q + (int64_t)q_row * p.q_row_stride + (int64_t)h0 * HD;
-        for (int idx = tid; idx < 16 * CH; idx += 128) {
-            int row = idx / CH, c = idx - row * CH;
-            bool ok = row < nh;
-            cp_async16(Qs + row * SD + c * 8, ok ? qsrc + (int64_t)row * HD + c * 8 : qsrc, ok ? 16 : 0);
-        }
-        if (f.on) cp_async_commit();  // a group of their own: they are needed before the first keys are
-    }
     int lo_pos = 0;
     if (p.window > 0) {
         lo_pos = pos - p.window + 1;
@@ -342,16 +333,30 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
         load_page<HD>(st, kbase + off, tid, 128);
         load_page<HD>(st + 64 * SD, vbase + off, tid, 128);
     };
+    // Without `f.on` the keys of this step were written by the kernel just ahead: nothing is fetched early.
+    if (!f.on) pdl_wait();
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; s++) {
         if (s < n) load_tile(s);
+        cp_async_commit();
+    }
+    if (f.on) pdl_wait();
+    pdl_trigger();  // the product that follows may start fetching its weights
+    {
+        constexpr int CH = HD / 8;
+        const bf16* qsrc = (const bf16*)p.q + (int64_t)q_row * p.q_row_stride + (int64_t)h0 * HD;
+        for (int idx = tid; idx < 16 * CH; idx += 128) {
+            int row = idx / CH, c = idx - row * CH;
+            bool ok = row < nh;
+            cp_async16(Qs + row * SD + c * 8, ok ? qsrc + (int64_t)row * HD + c * 8 : qsrc, ok ? 16 : 0);
+        }
         cp_async_commit();
     }
 
     // The CTA whose keys end with the token's own page has that key and value from the q/k/v product's
     // row, not from the cache: the last tile is patched in shared memory, and one CTA per kv head also
     // stores them in the cache for the steps to come.
-    const bool owns_last = f.on && n > 0 && my_hi == t_hi;
+    const bool owns_last = f.on && f.write_kv && n > 0 && my_hi == t_hi;  // a run that only reads another's cache finds the key there
     if (f.on && n > 0) {
         const int half = f.rot / 2;
         // rows whose position lies beyond the table are refused on the host
@@ -364,7 +369,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
             const bf16* vsrc = row + (int64_t)(p.heads + p.kv_heads + kvh) * HD;
             for (int i = tid; i < 2 * HD; i += 128) fresh[i] = i < HD ? ksrc[i] : vsrc[i - HD];
         }
-        cp_async_wait<DSTAGES - 1>();  // the queries have landed; the first tiles may still be on their way
+        cp_async_wait<0>();  // the queries have landed (the first tiles were requested before them)
         __syncthreads();
         for (int task = warp; task < nh + (owns_last ? 1 : 0); task += 4) {
             if (task < nh)
@@ -373,7 +378,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
                 norm_rope_row<HD>(fresh, Ys + warp * HD, f.k_w, f.eps, cs, sn, f.rot, lane, f.consecutive != 0);
         }
         __syncthreads();
-        if (owns_last && chunk == 0 && f.write_kv) {
+        if (owns_last && chunk == 0) {
             const int64_t page = page_of(bt, pos, p.bt_stride, p.pages);
             const int64_t at = ((page * p.kv_heads + kvh) * 64 + (pos & 63)) * (int64_t)HD;
             bf16* kdst = (bf16*)p.k_plane + at;
@@ -397,7 +402,11 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
     uint32_t qf[QREG ? KS : 1][4];
 
     for (int i = 0; i < n; i++) {
-        cp_async_wait<DSTAGES - 2>();
+        // tile i has landed; the queries, requested last, only once every group has (first iteration)
+        if (i == 0)
+            cp_async_wait<0>();
+        else
+            cp_async_wait<DSTAGES - 2>();
         __syncthreads();
         if (i + DSTAGES - 1 < n) load_tile(i + DSTAGES - 1);
         cp_async_commit();
@@ -575,9 +584,10 @@ int launch_decode(const AttnParams& p, const RopeFuse& f, cudaStream_t stream) {
     const int hchunks = (G + GC - 1) / GC;
     dim3 grid(p.num_splits, p.kv_heads * hchunks, p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("attention_decode_mma: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
-    // Measured at 8 and 64 sequences of 4096 keys: launched early, this kernel gains a little when it
+    // Measured at 1 to 64 sequences of 4096 keys: launched early, this kernel gains a little when it
     // is alone (one split, many CTAs) and loses when its CTAs and those of the merge behind it sit
-    // waiting beside the kernels ahead, so only the single-split form is a dependent launch.
+    // waiting beside the kernels ahead (also when it fetches its first pages while it waits), so only
+    // the single-split form is a dependent launch.
     if (p.num_splits == 1)
         launch_pdl(attn_decode_mma_kernel<HD, QREG>, grid, dim3(128), (size_t)smem, stream, p, f);
     else

@@ -248,13 +248,19 @@ GB_API int gb_prenorm_layer_forward(const GbPrenormLayer* Lp, const GbStepRows* 
     QkRopeParams r = {ws.qkv, qkv_dim, L.q_norm_w, L.k_norm_w, L.qk_norm_eps, L.cos_t, L.sin_t, L.rotary_dim, L.table_positions,
                       S.row_pos, S.row_seq, S.seq_slot, S.block_table, S.bt_stride, S.k_plane, S.v_plane, S.write_kv,
                       rows, L.heads, L.kv_heads, L.head_dim, S.pages, S.max_slots};
-    GB_TRY(gb_qk_norm_rope_kv_write(&r, act, stream));
-    n++;
     AttnParams a = {ws.qkv, qkv_dim, ws.ctx, q_dim, S.k_plane, S.v_plane, S.block_table, S.bt_stride, S.seq_slot, S.seq_q_start,
                     S.seq_q_len, S.seq_kv_len, S.nseq, L.heads, L.kv_heads, L.head_dim, S.max_q_len, L.scale, L.window,
                     S.num_splits > 1 ? S.num_splits : 1, S.num_splits > 1 ? S.split_scratch : nullptr, S.pages, S.max_slots};
-    GB_TRY(gb_attention_auto(&a, act, rows, S.pages, &algo, &kernels, stream));
-    n += kernels;
+    if (gb_attention_decode_rope_accepts(act, L.head_dim, L.rotary_dim, S.max_q_len) && rows == S.nseq) {
+        // single tokens: the attention kernel norms and rotates its queries and places the token's key and value itself
+        GB_TRY(gb_attention_decode_mma_rope(&a, &r, stream));
+        n += a.num_splits > 1 ? 2 : 1;
+    } else {
+        GB_TRY(gb_qk_norm_rope_kv_write(&r, act, stream));
+        n++;
+        GB_TRY(gb_attention_auto(&a, act, rows, S.pages, &algo, &kernels, stream));
+        n += kernels;
+    }
     // output projection: into the residual itself where the paired-SM kernel takes it, else an addend for the next norm
     const float* mixed = nullptr;
     if (gb_gemm_add_accepts(ws.ctx, act, L.w_o, L.w_o_dtype, h, rows, L.hidden, q_dim, q_dim, L.hidden, sms) && (L.hidden & 3) == 0) {

@@ -543,11 +543,12 @@ def test_attention_single_tokens(ops, dtype, algo, heads, kvh, d, splits):
 @pytest.mark.parametrize("heads,kvh,d,rot", [(4, 2, 16, 16), (5, 1, 48, 32), (32, 8, 128, 128), (8, 2, 128, 64), (20, 1, 32, 0), (2, 2, 256, 256),
                                               (40, 2, 64, 64), (6, 3, 112, 112)])
 @pytest.mark.parametrize("splits", [1, 3, 8])
-@pytest.mark.parametrize("normed", [True, False])
-def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, heads, kvh, d, rot, splits, normed):
+@pytest.mark.parametrize("normed,write", [(True, True), (False, True), (True, False)])
+def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, heads, kvh, d, rot, splits, normed, write):
     """One kernel instead of two: the queries are normed and rotated by the attention kernel, the
     token's own key and value come from the q/k/v row and are stored in the cache.  The output and
-    the cache afterwards are the bits the two kernels one after the other give."""
+    the cache afterwards are the bits the two kernels one after the other give; a run that does not
+    write the cache (it reads another run's) finds the key of its position there."""
     kv_lens = [1, 64, 65, 700, 333, 128]
     nseq = len(kv_lens)
     assert ops.attention_decode_rope_accepts(torch.bfloat16, d, rot, 1)
@@ -566,7 +567,7 @@ def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, he
     for fused in (False, True):
         qkv, k, v = qkv0.clone(), k0.clone(), v0.clone()
         out = torch.full((nseq, heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-        rope_args = (heads, kvh, d, qw, kw, 1e-6, cos, sin, rot, pos, seqs, slots, table, k, v, True)
+        rope_args = (heads, kvh, d, qw, kw, 1e-6, cos, sin, rot, pos, seqs, slots, table, k, v, write)
         attn_args = (k, v, table, slots, mk(range(nseq)), mk([1] * nseq), mk(kv_lens), nseq, 1, heads, kvh, d, d ** -0.5, 0, splits, scratch)
         if fused:
             ops.attention_decode_rope(qkv, out, rope_args, attn_args)
@@ -578,7 +579,7 @@ def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, he
     (out_a, k_a, v_a), (out_b, k_b, v_b) = results
     assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
     assert torch.equal(out_a, out_b)
-    assert not torch.equal(k_a, k0)
+    assert torch.equal(k_a, k0) != write and torch.equal(v_a, v0) != write
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
