@@ -342,7 +342,7 @@ def probe(name, **opts):
                 state["i"] += 1
         work = N * K * 2.0
         unit = "GB/s"
-    elif name in ("attn_decode_b8", "attn_decode_b64", "attn_prefill"):
+    elif name in ("attn_decode_b8", "attn_decode_b64", "attn_decode_rope_b8", "attn_prefill"):
         heads, kvh, d = 32, 8, 128
         if name == "attn_prefill":
             nseq, q_len, kv_len = 1, 2048, 2048
@@ -364,6 +364,19 @@ def probe(name, **opts):
 
         def fn():
             ops.attention(q, out, k, v, table, slot, start, ql, kl, nseq, q_len, heads, kvh, d, d ** -0.5, 0, splits, scratch)
+        if name == "attn_decode_rope_b8":
+            # as a decode step calls it: rows as the q/k/v product left them; the kernel norms and rotates
+            # its queries, takes the token's key and value from the row and stores them in the cache
+            qkv = rnd(nseq, (heads + 2 * kvh) * d)
+            out = torch.empty((nseq, heads * d), dtype=bf, device=dev)
+            w = torch.ones(d, device=dev)
+            angles = torch.rand(kv_len, d // 2, device=dev)
+            cos, sin = torch.cos(angles), torch.sin(angles)
+            rope_args = (heads, kvh, d, w, w, 1e-6, cos, sin, d, ints([kv_len - 1] * nseq), slot, slot, table, k, v, True)
+            attn_args = (k, v, table, slot, start, ql, kl, nseq, 1, heads, kvh, d, d ** -0.5, 0, splits, scratch)
+
+            def fn():
+                ops.attention_decode_rope(qkv, out, rope_args, attn_args)
         if q_len == 1:
             work, unit = 2.0 * n_pages * kvh * 64 * d * 2, "GB/s"
         else:
@@ -415,7 +428,8 @@ def probe(name, **opts):
 
 
 KERNEL_PROBES = ("gemm_prefill", "gemm_prefill_swiglu", "attn_prefill", "gemm_decode_b8", "gemm_scaled_b8", "gemm_residual_b8",
-                 "gemm_decode_b64", "gemm_scaled_b64", "gemm_residual_b64", "gemm_down_b128", "attn_decode_b8", "attn_decode_b64")
+                 "gemm_decode_b64", "gemm_scaled_b64", "gemm_residual_b64", "gemm_down_b128", "attn_decode_b8", "attn_decode_rope_b8",
+                 "attn_decode_b64")
 
 
 def profile():
