@@ -487,6 +487,100 @@ __global__ void __launch_bounds__(256) qk_rope_bf16_d128_kernel(QkRopeParams p) 
     }
 }
 
+// The same geometry for prompts (many rows): half a warp per head and row, a lane holds eight
+// consecutive elements (16-byte loads and stores), element i and its partner i + 64 sit in lanes l
+// and l ^ 8 of the half.  Fewer instructions per element than the kernel above, which is bound by its
+// instruction stream once there are rows enough to fill the GPU (2048 rows of 48 heads: 18.4 -> 15.0
+// us; with several heads of a row per half warp, to load the row's angles once, 16.2).  A warp takes
+// two heads of WIDE_ROWS consecutive rows.
+constexpr int WIDE_ROWS = 4;
+
+__global__ void __launch_bounds__(256) qk_rope_bf16_d128_wide_kernel(QkRopeParams p) {
+    pdl_wait();
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, l16 = lane & 15;
+    const int r0 = blockIdx.x * WIDE_ROWS;
+    const int total_heads = p.heads + 2 * p.kv_heads;
+    int head = (blockIdx.y * 8 + warp) * 2 + (lane >> 4);
+    const bool live = head < total_heads;  // a dead half takes part in the shuffles and stores nothing
+    if (!live) head = total_heads - 1;
+    typedef __nv_bfloat16 bf;
+    const bool is_q = head < p.heads;
+    const bool is_k = !is_q && head < p.heads + p.kv_heads;
+    const bool stores = live && (is_q || p.write_kv);
+    const int kvh = is_q ? 0 : (is_k ? head - p.heads : head - p.heads - p.kv_heads);
+    const float* w = is_q ? p.q_w : p.k_w;
+    const int ci = (l16 & 7) * 8;  // index into the 64 angles of a position
+
+    int pos[WIDE_ROWS];
+    uint4 raw[WIDE_ROWS];
+    bf* dst[WIDE_ROWS];
+#pragma unroll
+    for (int j = 0; j < WIDE_ROWS; j++) {
+        const int r = r0 + j < p.rows ? r0 + j : p.rows - 1;  // rows past the end repeat the last one and are not stored
+        pos[j] = p.row_pos[r];
+        bf* src = (bf*)p.qkv + (int64_t)r * p.row_stride + (int64_t)head * 128 + l16 * 8;
+        raw[j] = *reinterpret_cast<const uint4*>(src);
+        dst[j] = src;
+    }
+    if (!is_q) {
+#pragma unroll
+        for (int j = 0; j < WIDE_ROWS; j++) {
+            const int r = r0 + j < p.rows ? r0 + j : p.rows - 1;
+            const int slot = p.seq_slot[p.row_seq[r]];
+            const int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot, p.max_slots), pos[j], p.bt_stride, p.pages);
+            bf* plane = (bf*)(is_k ? p.k_plane : p.v_plane);
+            dst[j] = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos[j] % GB_PAGE)) * (int64_t)128 + l16 * 8;
+        }
+    }
+    const bool value = !is_q && !is_k;
+    const bool normed = w != nullptr && !value;
+    float ww[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) ww[e] = 1.f;
+    if (normed) {
+        const float4 a = *reinterpret_cast<const float4*>(w + l16 * 8), b = *reinterpret_cast<const float4*>(w + l16 * 8 + 4);
+        ww[0] = a.x; ww[1] = a.y; ww[2] = a.z; ww[3] = a.w; ww[4] = b.x; ww[5] = b.y; ww[6] = b.z; ww[7] = b.w;
+    }
+#pragma unroll
+    for (int j = 0; j < WIDE_ROWS; j++) {
+        const uint32_t in[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&in[e]);
+            y[2 * e] = __low2float(h2);
+            y[2 * e + 1] = __high2float(h2);
+        }
+        // the halves of a warp may hold heads of different kinds: both run the same instructions and choose at the end
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += y[e] * y[e];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = normed ? 1.0f / sqrtf(ss / 128.f + p.eps) : 1.f;
+        const int tpos = gb_check(pos[j], p.table_positions, GB_CHECK_ROPE_POSITION) ? pos[j] : 0;
+        const float4 c0 = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)tpos * 64 + ci), c1 = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)tpos * 64 + ci + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)tpos * 64 + ci), s1 = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)tpos * 64 + ci + 4);
+        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        uint32_t out[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float o2[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int i = 2 * e + u;
+                const float v = normed ? y[i] * inv * ww[i] : y[i];
+                const float partner = __shfl_xor_sync(0xffffffffu, v, 8);
+                o2[u] = l16 < 8 ? v * cs[i] - partner * sv[i] : v * cs[i] + partner * sv[i];
+            }
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(o2[0], o2[1]);
+            out[e] = value ? in[e] : *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        if (stores && r0 + j < p.rows) *reinterpret_cast<uint4*>(dst[j]) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
 GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStream_t stream) {
     QkRopeParams p = *pp;
     if (p.rows <= 0) return 0;
@@ -499,6 +593,13 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     if (dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
         !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
         ceil_div(total_heads, 8) <= 65535) {
+        // prompts: the kernel of 16-byte accesses (it adds a row's squares up in another order, so a key
+        // may differ in its last bit from the one the kernel for few rows would write)
+        if (p.rows >= 256 && !(p.row_stride & 7) && !((uintptr_t)p.qkv & 15)) {
+            launch_pdl(qk_rope_bf16_d128_wide_kernel, dim3(ceil_div(p.rows, WIDE_ROWS), ceil_div(total_heads, 16)), dim3(256), 0, stream, p);
+            GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
+            return 0;
+        }
         launch_pdl(qk_rope_bf16_d128_kernel, dim3(ceil_div(p.rows, ROPE_ROWS), ceil_div(total_heads, 8)), dim3(256), 0, stream, p);
         GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
         return 0;

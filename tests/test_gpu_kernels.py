@@ -367,17 +367,18 @@ def gather_kv(plane, table_row, length):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kvh,d,rot,qk_norm", [(4, 2, 16, 16, True), (5, 1, 48, 48, True), (6, 3, 32, 16, True),
                                                     (2, 2, 128, 128, False), (3, 1, 80, 0, True), (5, 2, 128, 128, True), (2, 1, 128, 64, True)])
-def test_qk_norm_rope_kv_write(ops, dtype, heads, kvh, d, rot, qk_norm):
+@pytest.mark.parametrize("lens", [[3, 70, 1], [3, 300, 1]])   # rows per sequence in this step; many rows: the prompt kernels
+def test_qk_norm_rope_kv_write(ops, dtype, heads, kvh, d, rot, qk_norm, lens):
     eps, theta = 2e-6, 5000.0
-    lens = [3, 70, 1]           # rows per sequence in this step
     past = [0, 60, 130]         # tokens already cached
     slots = [2, 0, 5]
     rows = sum(lens)
-    n_pages, max_pages = 16, 4
+    max_pages = (max(p + n for p, n in zip(past, lens)) + 63) // 64 + 1
+    n_pages = 3 * max_pages + 4
     perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
     table = torch.zeros((6, max_pages), dtype=torch.int32)
     for i, s in enumerate(slots):
-        table[s] = perm[i * 4:(i + 1) * 4]
+        table[s] = perm[i * max_pages:(i + 1) * max_pages]
     table = table.to(DEV)
     k_plane, v_plane = paged(n_pages, kvh, d, dtype, 3)
     k0, v0 = k_plane.clone(), v_plane.clone()
@@ -389,7 +390,7 @@ def test_qk_norm_rope_kv_write(ops, dtype, heads, kvh, d, rot, qk_norm):
     seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
     cos = sin = None
     if rot:
-        c, s = P.rope_tables(np.arange(256), rot, theta)
+        c, s = P.rope_tables(np.arange(512), rot, theta)
         cos, sin = (torch.tensor(x, dtype=torch.float32, device=DEV) for x in (c, s))
     ops.qk_norm_rope_kv_write(qkv, heads, kvh, d, qw, kw, eps, cos, sin, rot, row_pos, row_seq, seq_slot,
                               table, k_plane, v_plane, True)
