@@ -1,6 +1,6 @@
 // The few-row product (gemm_skinny.cu: up to 8 rows, weights streamed from global memory straight
 // into tensor-core fragments, K split over the warps of a CTA) with the residual stream's two
-// row-wise kernels folded into it, so that a decode layer runs seven kernels instead of nine
+// row-wise kernels folded into it, so that a decode layer runs without its two norm kernels
 // (the reference's decode layer folds its norms the same way: the producer's epilogue adds into
 // the residual and publishes partial sums of squares, the consumer applies the RMSNorm factor from
 // them: internal/qwen3lm/gpu.metal:70-162).

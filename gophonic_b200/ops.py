@@ -415,9 +415,9 @@ _ALGO_NAMES = ("simt", "skinny", "tc5", "tc5_pair", "tc5_decode")
 
 def gemm_algo(M: int, N: int, K: int) -> str:
     """The tensor-core kernel ``gemm`` picks for aligned bfloat16 operands of these sizes: up to 8 rows
-    the fragment-streaming kernel, up to 128 (256 for narrow outputs with a long K) the tcgen05
-    decode kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs two SMs
-    on a tile.  The rule lives in the library (``gb_gemm_algo``), which also applies it when it
+    the fragment-streaming kernel, up to 64 rows (128 or 256 for narrow outputs) the tcgen05 decode
+    kernel, otherwise the tiled tcgen05 kernel and from 192 rows the one that pairs two SMs on a
+    tile.  The rule lives in the library (``gb_gemm_algo``), which also applies it when it
     issues a whole layer itself."""
     return _ALGO_NAMES[int(_lib.gb_gemm_algo(c_int(M), c_int(N), c_int(K), c_int(_sms())))]
 

@@ -174,7 +174,7 @@ class Mixer(Part):
         ``norm``), applies the rows' factors from the statistics in its first product, adds its
         output into the float32 residual ``h`` in its last product and returns the new ``RowStats``,
         prescaled for ``next_norm`` if that is given and can be.  Only offered where it is faster
-        (single-token steps of a few rows); the default is False."""
+        (single-token steps of up to 64 rows); the default is False."""
         return False
 
     def adds_in_place(self, rows: int) -> bool:

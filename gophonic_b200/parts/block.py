@@ -6,7 +6,7 @@ built-in parts: ``adds_in_place``), or it is not added at once: it is handed on 
 addend and added by whatever norms the residual next (the layer's second norm, the next block's
 first norm, or the final norm), in the same kernel that takes the statistics
 (internal/qwen3lm/evaluator.go:641-647, 678-682; ops.go:94-108 does the same).  In single-token
-steps of a few rows the built-in parts go one step further (``folds_norm``): the part's last
+steps of up to 64 rows the built-in parts go one step further (``folds_norm``): the part's last
 product adds into the residual, leaves the rows' sums of squares behind and writes the rows
 already multiplied by the next norm's weight (``RowStats``), and the next part's first product
 multiplies its finished sums by the rows' factors, so no norm kernel runs at all
