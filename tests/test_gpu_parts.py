@@ -512,23 +512,26 @@ def mixed_plain(toks, cfg: MixedConfig, w):
     return P.rms_norm(h, w["m.norm.weight"], cfg.rms_norm_eps) @ w["m.head.weight"].T
 
 
-def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_layer_by_layer(tmp_path):
+@pytest.mark.parametrize("dtype,experts", [("float32", 3), ("bfloat16", 1)])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_layer_by_layer(tmp_path, dtype, experts):
     """Two layers whose parts differ: the registry builds each from its spec's kind, the loader and
     the random-weights writer work from the parts' declarations, the engine steps prompts and
-    single tokens, and the logits are those of a plain restatement.  In 32-bit, where the router's
-    choice cannot flip on rounding."""
+    single tokens, and the logits are those of a plain restatement.  In 32-bit with three experts;
+    in bfloat16 with one, where no choice can flip on rounding: there the built-in parts fold their
+    norms into their products in single-token steps and the toy part, which does not, sits between
+    them, and the attention kernel rotates by the toy encoding's tables itself."""
     from gophonic_b200 import registry
     from gophonic_b200.engine import Engine, Model
     from gophonic_b200.weights import InitScales, write_random_model
     registry.register_feed_forward("toy-top1", _routed_ffn())
     registry.register_position("toy-slow-rope", _slow_rope())
     registry.register_architecture("ToyMixedForCausalLM", MixedConfig, model_type="toy_mixed")
-    cfg = MixedConfig(hidden_size=64, heads=4, kv_heads=2, head_dim=16, intermediate_size=96, experts=3, inner=40, vocab_size=211,
+    cfg = MixedConfig(hidden_size=64, heads=4, kv_heads=2, head_dim=16, intermediate_size=96, experts=experts, inner=40, vocab_size=211,
                       theta=10000.0, slowdown=4.0, rms_norm_eps=1e-5)
     d = str(tmp_path / "mixed")
     write_random_model(cfg, 5, d, scales=InitScales(**TEST_SCALES))
     assert registry.read_config(d) == cfg
-    model = Model.from_dir(d, dtype="float32")
+    model = Model.from_dir(d, dtype=dtype)
     assert not model.capturable  # the routed part reads device values on the host: steps run eagerly
     eng = Engine(model, max_tokens=1024)
     _, w = P.read_model(d)
@@ -549,6 +552,6 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_layer_by_layer(tm
             got[i].append(out[j:j + 1])
         step += 1
     for i in range(3):
-        assert rel(np.concatenate(got[i], 0), refs[i]) < TOL[torch.float32], i
+        assert rel(np.concatenate(got[i], 0), refs[i]) < TOL[torch.float32 if dtype == "float32" else torch.bfloat16], i
         eng.end_sequence(slots[i])
     eng.cache.check()
