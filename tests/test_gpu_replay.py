@@ -684,3 +684,46 @@ def test_random_configurations_and_plans(trial, tmp_path):
                 live = [i for i in live if step < plans[i][1]]
             eng.cache.check()
             assert eng.cache.pages.held() == 0
+
+
+@pytest.mark.parametrize("trial", range(4))
+def test_random_configurations_decoding_many_sequences(trial, tmp_path):
+    """Seeded random sizes as above, with 9 to 64 sequences decoding together: the row counts at which
+    single-token steps run on the tcgen05 decode kernel with the norms folded into its products
+    (where the sizes allow it) and are replayed at a few captured batch sizes."""
+    from gophonic_b200.config import Qwen3Config
+    from gophonic_b200.engine import Engine, Model
+    from gophonic_b200.weights import InitScales, write_random_model
+    rng = np.random.default_rng(5000 + trial)
+    kvh = int(rng.choice([1, 2, 3, 4]))
+    cfg = Qwen3Config(hidden_size=int(rng.choice([40, 72, 96, 136, 200, 256, 384])), num_hidden_layers=int(rng.choice([1, 2, 3])),
+                      num_attention_heads=kvh * int(rng.choice([1, 2, 3, 5, 8])), num_key_value_heads=kvh,
+                      head_dim=int(rng.choice([16, 48, 64, 80, 128])), intermediate_size=int(rng.choice([24, 66, 136, 160, 520])),
+                      vocab_size=int(rng.choice([23, 257, 1000, 3001])), max_position_embeddings=1024,
+                      rms_norm_eps=float(rng.choice([1e-6, 1e-5])), rope_theta=float(rng.choice([1e4, 1e6])),
+                      tie_word_embeddings=bool(rng.integers(0, 2)))
+    mdir = str(tmp_path / "model")
+    write_random_model(cfg, seed=trial, out_dir=mdir, weight_dtype="bfloat16", scales=InitScales(matrix=0.1, embedding=1.0, head=0.1, norm=0.1))
+    pc, pw = P.read_model(mdir)
+    nseq = [13, 40, 64, 24][trial]
+    plans = [(int(rng.choice([1, 2, 7, 20, 33, 64, 65, 70])), int(rng.integers(1, 5))) for _ in range(nseq)]
+    toks = [rng.integers(0, cfg.vocab_size, size=p + n).tolist() for p, n in plans]
+    refs = [P.forward_logits(t, pc, pw) for t in toks]
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(Model.from_dir(mdir, dtype=dtype), max_tokens=16384)
+        slots = [eng.new_sequence() for _ in plans]
+        got = eng.step([(s, t[:p]) for s, t, (p, n) in zip(slots, toks, plans)], [[p - 1] for p, n in plans]).cpu().numpy()
+        for i, (p, n) in enumerate(plans):
+            assert float(np.max(np.abs(got[i] - refs[i][p - 1])) / np.max(np.abs(refs[i]))) < TOL[dtype], (cfg, dtype, "prompt", i)
+        live, step = list(range(nseq)), 0
+        while live:
+            got = eng.step([(slots[i], [toks[i][plans[i][0] + step]]) for i in live]).cpu().numpy()
+            for j, i in enumerate(live):
+                ref = refs[i][plans[i][0] + step]
+                assert float(np.max(np.abs(got[j] - ref)) / np.max(np.abs(refs[i]))) < TOL[dtype], (cfg, dtype, len(live), i, step)
+            step += 1
+            for i in [i for i in live if step >= plans[i][1]]:
+                eng.end_sequence(slots[i])
+            live = [i for i in live if step < plans[i][1]]
+        eng.cache.check()
+        assert eng.cache.pages.held() == 0
