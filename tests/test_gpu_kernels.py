@@ -544,8 +544,8 @@ def test_attention_single_tokens(ops, dtype, algo, heads, kvh, d, splits):
 @pytest.mark.parametrize("heads,kvh,d,rot", [(4, 2, 16, 16), (5, 1, 48, 32), (32, 8, 128, 128), (8, 2, 128, 64), (20, 1, 32, 0), (2, 2, 256, 256),
                                               (40, 2, 64, 64), (6, 3, 112, 112)])
 @pytest.mark.parametrize("splits", [1, 3, 8])
-@pytest.mark.parametrize("normed,write", [(True, True), (False, True), (True, False)])
-def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, heads, kvh, d, rot, splits, normed, write):
+@pytest.mark.parametrize("normed,write,window", [(True, True, 0), (False, True, 0), (True, False, 0), (True, True, 100)])
+def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, heads, kvh, d, rot, splits, normed, write, window):
     """One kernel instead of two: the queries are normed and rotated by the attention kernel, the
     token's own key and value come from the q/k/v row and are stored in the cache.  The output and
     the cache afterwards are the bits the two kernels one after the other give; a run that does not
@@ -569,7 +569,7 @@ def test_single_token_attention_that_rotates_and_stores_the_token_itself(ops, he
         qkv, k, v = qkv0.clone(), k0.clone(), v0.clone()
         out = torch.full((nseq, heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
         rope_args = (heads, kvh, d, qw, kw, 1e-6, cos, sin, rot, pos, seqs, slots, table, k, v, write)
-        attn_args = (k, v, table, slots, mk(range(nseq)), mk([1] * nseq), mk(kv_lens), nseq, 1, heads, kvh, d, d ** -0.5, 0, splits, scratch)
+        attn_args = (k, v, table, slots, mk(range(nseq)), mk([1] * nseq), mk(kv_lens), nseq, 1, heads, kvh, d, d ** -0.5, window, splits, scratch)
         if fused:
             ops.attention_decode_rope(qkv, out, rope_args, attn_args)
             assert torch.equal(qkv, qkv0)          # the rows stay as the product left them
