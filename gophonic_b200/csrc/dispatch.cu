@@ -27,6 +27,11 @@ constexpr int TC5_PAIR_MIN_ROWS = 192;
 constexpr int WIDE_OUTPUT = 32768;
 // prompts whose longest sequence brings at least this many rows use the tcgen05 attention kernel
 constexpr int TC5_ATTENTION_MIN_ROWS = 65;
+// few-row products of at least this many weights, and at least this long on both sides, run on the tcgen05
+// decode kernel (inside a decode step of 8B sizes the 24576 x 4096 product, a little faster there by
+// itself, cost the step a quarter: the width that counts is the one of the products around it as well)
+constexpr int64_t BIG_PRODUCT = 40 << 20;
+constexpr int BIG_PRODUCT_MIN_SIDE = 5120;
 
 GB_API int gb_dispatch_constant(int which) {
     switch (which) {
@@ -44,7 +49,12 @@ GB_API int gb_dispatch_constant(int which) {
 // of a layer at 1.7B, 8B and 32B sizes, 1 to 2048 rows).
 GB_API int gb_gemm_algo(int M, int N, int K, int sms) {
     (void)K;
-    if (M <= SKINNY_MAX_ROWS && N < WIDE_OUTPUT) return GB_ALGO_SKINNY;  // weights streamed straight into mma.sync fragments
+    // Few rows: the weights streamed straight into mma.sync fragments, except for the largest products, which
+    // the tcgen05 decode kernel streams faster (one row, us: 10240 x 5120 18.4 against 21.1, 5120 x 8192 16.2
+    // against 17.8, 5120 x 25600 41.0 against 49.4; but 4096 x 12288 18.7 against 17.5 and 6144 x 4096 10.6
+    // against 9.8)
+    const bool large = (int64_t)N * K >= BIG_PRODUCT && N >= BIG_PRODUCT_MIN_SIDE && K >= BIG_PRODUCT_MIN_SIDE;
+    if (M <= SKINNY_MAX_ROWS && N < WIDE_OUTPUT && !large) return GB_ALGO_SKINNY;
     // tcgen05, weights on the M side, K slices across a cluster; a head-sized output has tiles enough for the
     // tiled kernel, which reads the activations once per 256 columns (151936 x 4096 at 64 rows: 222 against 241 us)
     if (M <= 64) return N >= WIDE_OUTPUT && M > 16 ? GB_ALGO_TC5 : GB_ALGO_TC5_DECODE;

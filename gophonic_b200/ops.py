@@ -303,7 +303,7 @@ def gemm_scaled(x: torch.Tensor, eps: float, stats: torch.Tensor, stats_count: i
             or out.shape != (M, N // 2 if swiglu else N) or stats.shape[0] < M or not 0 < stats_count <= stats.shape[1]):
         raise KernelError(f"gemm_scaled: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
                           f"{stats_count} partial sums in {tuple(stats.shape)}")
-    if M <= SKINNY_MAX_ROWS and N < WIDE_OUTPUT:   # the kernels ``gemm`` picks: fragment streaming, else tcgen05 decode
+    if gemm_algo(M, N, K) == "skinny":   # the kernel ``gemm`` picks: fragment streaming, else tcgen05 decode
         _check(_lib.gb_gemm_skinny_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
                                           c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
                                           c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream()))
@@ -335,7 +335,7 @@ def gemm_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, stats: torc
     if not gemm_residual_accepts(x, w, h) or w.shape[1] != K or h.shape != (M, N) or stats.shape[0] < M or stats.shape[1] < count:
         raise KernelError(f"gemm_residual: x {tuple(x.shape)}, w {tuple(w.shape)}, h {tuple(h.shape)}, statistics {tuple(stats.shape)}")
     ldxn = _check_next(next_weight, next_x, M, N, "gemm_residual")
-    if M <= SKINNY_MAX_ROWS:
+    if gemm_algo(M, N, K) == "skinny":
         _check(_lib.gb_gemm_skinny_residual(_ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(h), c_int64(h.stride(0)), _ptr(stats),
                                             c_int64(stats.stride(0)), _ptr(next_weight), _ptr(next_x), c_int64(ldxn),
                                             c_int(M), c_int(N), c_int(K), _stream()))
