@@ -48,7 +48,6 @@ GB_API int gb_dispatch_constant(int which) {
 // The tensor-core kernel for aligned bfloat16 operands of these sizes (measured on the four products
 // of a layer at 1.7B, 8B and 32B sizes, 1 to 2048 rows).
 GB_API int gb_gemm_algo(int M, int N, int K, int sms) {
-    (void)K;
     // Few rows: the weights streamed straight into mma.sync fragments, except for the largest products, which
     // the tcgen05 decode kernel streams faster (one row, us: 10240 x 5120 18.4 against 21.1, 5120 x 8192 16.2
     // against 17.8, 5120 x 25600 41.0 against 49.4; but 4096 x 12288 18.7 against 17.5 and 6144 x 4096 10.6
