@@ -117,7 +117,8 @@ def test_gemm_with_swiglu_epilogue(ops, M, inter, K, out_dtype):
 # ---- few-row products with the norm and the residual add folded in ---------------------------
 # up to 8 rows the fragment-streaming kernel, 9 to 64 the tcgen05 decode kernel (alone and in clusters of K slices)
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
-@pytest.mark.parametrize("N,K,count", [(64, 64, 1), (1000, 96, 5), (6144, 4096, 256), (136, 2048, 128), (40, 520, 33), (24576, 512, 7), (33024, 64, 3)])
+@pytest.mark.parametrize("N,K,count", [(64, 64, 1), (1000, 96, 5), (6144, 4096, 256), (136, 2048, 128), (40, 520, 33), (24576, 512, 7), (33024, 64, 3),
+                                       (5120, 8192, 40)])   # the last one is large enough for the tcgen05 decode kernel at every row count
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_that_applies_the_rows_norm_factors_from_statistics(ops, M, N, K, count, out_dtype):
     """out = rmsnorm(h) w^T where the rows arrive as bf16(h * norm weight) and each row's sum of
@@ -168,7 +169,7 @@ def test_gemm_that_applies_the_rows_norm_factors_with_the_swiglu_epilogue(ops, M
 
 
 @pytest.mark.parametrize("M", [1, 4, 8, 9, 16, 33, 64])
-@pytest.mark.parametrize("N,K", [(64, 64), (1000, 96), (4096, 12288), (4096, 4096), (40, 520), (5120, 1024), (19200, 128)])
+@pytest.mark.parametrize("N,K", [(64, 64), (1000, 96), (4096, 12288), (4096, 4096), (40, 520), (5120, 1024), (19200, 128), (5120, 8192)])
 def test_gemm_that_adds_into_the_residual_and_prepares_the_next_norm(ops, M, N, K):
     """h += x w^T in the product's own epilogue: the bits of the product into a buffer and a float32
     add; partial sums of squares of the new residual, one per block of columns (16 wide up to 8
@@ -176,14 +177,16 @@ def test_gemm_that_adds_into_the_residual_and_prepares_the_next_norm(ops, M, N, 
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
     h0, nw = rnd(M, N, seed=3), 1 + 0.1 * rnd(N, seed=4)
     prod = torch.empty((M, N), dtype=torch.float32, device=DEV)
-    ops.gemm(x, w, prod, algo="skinny" if M <= 8 else "tc5_decode")
+    algo = ops.gemm_algo(M, N, K)        # few rows: the fragment-streaming kernel, unless the product is large
+    assert algo == ("skinny" if M <= 8 and (N, K) != (5120, 8192) else "tc5_decode")
+    ops.gemm(x, w, prod, algo=algo)
     h = h0.clone()
     room = ops.fold_capacity(N)
     stats = torch.full((max(M, 8), room + 2), float("nan"), device=DEV)
     nxt = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     assert ops.gemm_residual_accepts(x, w, h)
     count = ops.gemm_residual(x, w, h, stats, nw, nxt)
-    block = 16 if M <= 8 else 128
+    block = 16 if algo == "skinny" else 128
     assert count == (N + block - 1) // block
     assert torch.equal(h, h0 + prod)
     close(h, h0.double() + x.double() @ w.double().T, 2e-5)
