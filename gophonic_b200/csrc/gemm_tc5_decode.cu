@@ -1,16 +1,18 @@
 // Y[M, N] = X[M, K] * W[N, K]^T for 9 to 256 rows on tcgen05: the product of a decode step, or of
 // a short prompt, when there are too many rows for the fragment-streaming kernel and too few for
-// the tiled kernels to give every SM a share of the weights.
+// the tiled kernels to give every SM a share of the weights.  (Also for fewer rows where the
+// dispatch rule finds it the faster stream: head-sized outputs, and products long on both sides.)
 //
 // The weights take the M side of the instruction: a CTA owns 128 rows of W and a slice of K, and
 // computes Y^T[128, batch] with UMMA M = 128, N = 16 / 32 / 64 / 128 / 256 (the batch rounded up;
 // TMA fills the missing rows of X with zeros).  Per K step of 64 a stage holds 16 KB of W from HBM
 // and 2 to 32 KB of X from L2; up to 64 rows four stages deep, above that three; two CTAs to an SM
 // (one at 256 columns), so every SM keeps tens of KB of weights in flight.  K is cut into slices so
-// that about that many CTAs exist even for narrow outputs.  The CTAs that share a tile (1, 2, 4 or 8 slices of K) form a thread-block cluster:
+// that about that many CTAs exist even for narrow outputs.  The CTAs that share a tile (1, 2, 4 or 8
+// slices of K) form a thread-block cluster:
 // each leaves its partial tile in its own shared memory, and after a cluster barrier each CTA adds
-// the slices, in slice order, for its share of the tile's rows, reading the other CTAs' shared
-// memory directly (distributed shared memory).  No scratch in global memory, and the sum does not
+// the slices, in slice order, for its share of the batch rows (a warp a row), reading the other CTAs'
+// shared memory directly (distributed shared memory).  No scratch in global memory, and the sum does not
 // depend on timing.  With the gate/up rows of a SwiGLU interleaved in blocks of eight the
 // activation is applied in the same epilogue.
 //
