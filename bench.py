@@ -520,6 +520,17 @@ def main():
     e2e = time_entry_point(model, args.batch, args.steps, max(warmup, 16), context, torch)
 
     extra_points = {}
+    if not args.no_points and args.model == "8b" and not args.layers and args.context == CONTEXT:
+        # a further context length: the same model, eight sequences of 32768 tokens (39 GB of keys and values)
+        long_context = 32768
+        engine = Engine(model, max_tokens=args.batch * long_context, max_slots=args.batch, max_seq_tokens=long_context)
+        fill_cache_random(engine, torch)
+        sampler = DeviceSampler(cfg.vocab_size, args.batch, engine.device)
+        run = time_decode(engine, sampler, args.batch, args.steps, 16, torch, ops)
+        long_bytes = weight_bytes + kv_bytes_per_token * run["kv_tokens"]
+        extra_points[f"decode_b{args.batch}_ctx{long_context}"] = round(args.batch / (run["ms"] * 1e-3), 1)
+        extra_points[f"decode_b{args.batch}_ctx{long_context}_hbm_frac"] = round(long_bytes / (run["ms"] * 1e-3) / 1e9 / hbm_peak, 4)
+        del engine, sampler
     if not args.no_points and args.model == "8b" and not args.layers:
         del model
         torch.cuda.empty_cache()
