@@ -6,11 +6,12 @@
 //     S_g = Q_g K^T   (M 128, N 64 keys, K 128)   -> two S buffers of 64 columns per group
 //     O_g += P_g V    (M 128, N 128, K 64 keys)    -> one O buffer of 128 columns per group
 // Roles by warp: warp 0 loads the query tiles once and per page two boxes of keys, the last warp per
-// page two boxes of values, by TMA straight from the paged cache, three pages deep each; one thread each of warps 1-2 issues the
+// page two boxes of values, by TMA straight from the paged cache, five pages deep each; one thread each of warps 1-2 issues the
 // scores products of group A and B and one each of warps 3-4 their values products; warps 5-8 and
 // 9-12 are the softmax of group A and B: each thread owns one query row, reads its row of S
 // from tensor memory, keeps the running maximum and sum, and writes the probabilities as bfloat16
-// into shared memory in the operand layout of the second product.  O stays in tensor memory and is
+// back into tensor memory, over the scores it has read, where the second product takes them as its
+// A operand (no shared memory, no proxy fence on the way).  O stays in tensor memory and is
 // rescaled only when a row's maximum has grown by more than 2^8 since the scale in use was chosen
 // (the final division by the row sum makes the choice of scale immaterial).  The scores of the
 // next page are issued before the probabilities of the current one are ready, and the two groups
@@ -31,13 +32,12 @@ namespace {
 __device__ int g_status;
 
 typedef __nv_bfloat16 bf16;
-constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 3, THREADS = 448;
+constexpr int HD = 128, BQ = 128, GROUPS = 2, BKV = 64, STAGES = 5, THREADS = 448;
 constexpr int FIRST_SOFTMAX_WARP = 1 + 2 * GROUPS;  // warp 0 loads queries and keys, then a scores issuer and a values issuer per group
 constexpr int VALUE_LOADER_WARP = FIRST_SOFTMAX_WARP + 4 * GROUPS;  // the last warp loads the values
 constexpr int QPANEL = 128 * 128;               // 128 rows of 128 bytes (64 head elements)
 constexpr int KPANEL = 64 * 128;                // 64 keys of 128 bytes
 constexpr int Q_BYTES = 2 * QPANEL;             // one group's query tile
-constexpr int P_BYTES = 128 * 128;              // one group's probabilities: 128 rows x 64 keys
 constexpr int K_BYTES = 2 * KPANEL, V_BYTES = 2 * KPANEL, STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr int TMEM_COLS = 512;                  // S: 2 groups x 2 buffers x 64; O: 2 groups x 128
 constexpr float LOG2E = 1.4426950408889634f;
@@ -58,6 +58,18 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr) {
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
+}
+
+// D (+)= A B with A in tensor memory (128 lanes, two bfloat16 a column) and B from shared memory
+__device__ __forceinline__ void umma_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -150,8 +162,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
-    unsigned char* Ps = Qs + GROUPS * Q_BYTES;         // [GROUPS][2][P_BYTES]
-    unsigned char* KVs = Ps + GROUPS * 2 * P_BYTES;    // [STAGES][K | V]
+    unsigned char* KVs = Qs + GROUPS * Q_BYTES;        // [STAGES][K | V]
     __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES];
     __shared__ uint64_t s_full[GROUPS][2], p_full[GROUPS][2], o_done[GROUPS][2];
     __shared__ uint32_t tmem_base_s;
@@ -324,9 +335,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                     ok = need_page(j);
                     if (ok && j < my_n) {
                         const int b = j & 1;
-                        // the softmax has read S of page j - 2 out of this buffer once it has announced
-                        // the probabilities of that page
-                        if (j >= 2) ok = mbar_wait_relaxed(&p_full[g][b], (uint32_t)((j - 2) >> 1) & 1u);
+                        // the probabilities of page j - 2 lie in this buffer's columns until their product has read them
+                        if (j >= 2) ok = mbar_wait_relaxed(&o_done[g][b], (uint32_t)((j - 2) >> 1) & 1u);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                         const uint64_t kd = k_desc[j % STAGES];
@@ -344,9 +354,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             } else {
                 // O_g (+)= P_g[j & 1] V_j, then the values of page j are free
                 const uint32_t idesc_pv = instr_desc(BQ, HD) | (1u << 16);  // values enter MN-major
-                uint64_t p_desc[2], v_desc[STAGES];
-                p_desc[0] = smem_desc(s32(Ps + (g * 2) * P_BYTES));
-                p_desc[1] = smem_desc(s32(Ps + (g * 2 + 1) * P_BYTES));
+                uint64_t v_desc[STAGES];
 #pragma unroll
                 for (int s = 0; s < STAGES; s++) v_desc[s] = smem_desc_mn(s32(KVs + (size_t)s * STAGE_BYTES + K_BYTES));
                 for (int j = 0; j < n && ok; j++) {
@@ -356,11 +364,14 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                         ok = mbar_wait(&p_full[g][b], (uint32_t)(j >> 1) & 1u);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                        const uint64_t pd = p_desc[b], vd = v_desc[j % STAGES];
+                        const uint64_t vd = v_desc[j % STAGES];
                         const uint32_t d_tmem = tmem_base + (uint32_t)(256 + g * 128);
 #pragma unroll
-                        for (int kk = 0; kk < BKV / 16; kk++)  // 16 keys = 16 rows of 128 bytes further into the values
-                            umma(d_tmem, pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        // 16 keys = 8 columns of the probabilities (written over the page's scores) and 16 rows of
+                        // 128 bytes further into the values
+                        for (int kk = 0; kk < BKV / 16; kk++)
+                            umma_ta(d_tmem, tmem_base + (uint32_t)(g * 128 + b * 64 + kk * 8), vd + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_pv,
+                                    (j > 0 || kk > 0) ? 1u : 0u);
                         umma_commit(&o_done[g][b]);
                     }
                     if (ok) umma_commit(&v_empty[j % STAGES]);
@@ -425,7 +436,6 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 break;
             }
 
-            unsigned char* Pg = Ps + (g * 2 + b) * P_BYTES;
             if (__any_sync(0xffffffffu, grow && j > 0)) {
                 // O_g may only be touched between products: wait for the previous page's
                 if (!mbar_wait(&o_done[g][(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1u)) {
@@ -449,6 +459,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             const float mbase = m_used == -INFINITY ? 0.f : m_used;
             const uint64_t sc2 = pack2(sc, sc), nmb2 = pack2(-mbase, -mbase);
             uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+            uint32_t pw[32];  // the row's 64 probabilities, two a word
 #pragma unroll
             for (int c = 0; c < 8; c++) {  // eight 16-byte chunks of eight keys
                 uint32_t pk[4];
@@ -468,16 +479,17 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                     pk[e] = *reinterpret_cast<uint32_t*>(&h2);
                 }
-                // K-major operand rows of 128 bytes (64 keys), groups of 8 rows, 128-byte swizzle
-                unsigned char* dst = Pg + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) pw[c * 4 + e] = pk[e];
             }
+            // The probabilities stay in tensor memory, as the A operand of the second product (128 lanes = rows,
+            // two bfloat16 a column): over the first 32 columns of this page's scores, which this thread has read out.
+            tmem_st32(s_addr, pw);
             float sum[4];
             unpack2(sum2[0], sum[0], sum[1]);
             unpack2(sum2[1], sum[2], sum[3]);
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[g][b]);
         }
@@ -550,7 +562,7 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (((uintptr_t)p.k_plane & 15) || ((uintptr_t)p.v_plane & 15)) GB_REFUSE("%s: cache planes must be 16-byte aligned", who);
     if (rows <= 0 || pages <= 0) GB_REFUSE("%s: %d rows, %d pages", who, rows, pages);
     if ((int64_t)pages * p.kv_heads * 64 > 0x7fffffff) GB_REFUSE("%s: the cache plane has too many rows for one tensor map", who);
-    const int smem = GROUPS * (Q_BYTES + 2 * P_BYTES) + STAGES * STAGE_BYTES + 1024;
+    const int smem = GROUPS * Q_BYTES + STAGES * STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
