@@ -70,6 +70,18 @@ GB_API int gb_gemm_algo(int M, int N, int K, int sms) {
     return GB_ALGO_TC5;                                                   // tcgen05, 128 x 256 tiles
 }
 
+// The kernel for a few-row product that applies row factors from statistics (the first product of a part
+// in a folded decode step).  As gb_gemm_algo, and the tcgen05 decode kernel also for a product as large as
+// the gate/up of an 8B layer (24576 x 4096: 34.0 against 37.7 us at eight rows), provided the few-row kernel
+// behind it is then launched as an ordinary kernel (see gb_gemm_skinny_residual): as a dependent launch it
+// would come in beside the decode kernel's CTAs one to an SM and run its other CTAs as a second wave.
+GB_API int gb_gemm_scaled_algo(int M, int N, int K, int sms) {
+    const int algo = gb_gemm_algo(M, N, K, sms);
+    // (whole 8B decode steps: 0.4 to 0.9 % slower at one to three sequences, 0.8 to 2.4 % faster at four to eight)
+    if (algo == GB_ALGO_SKINNY && M >= 4 && (int64_t)N * K >= BIG_PRODUCT && N >= BIG_PRODUCT_MIN_SIDE && K >= 4096) return GB_ALGO_TC5_DECODE;
+    return algo;
+}
+
 static bool tensor_core_operands(const void* A, int a_dtype, const void* W, int w_dtype, int K, int64_t lda) {
     return a_dtype == GB_BF16 && w_dtype == GB_BF16 && (K & 7) == 0 && (lda & 7) == 0 && !((uintptr_t)A & 15) && !((uintptr_t)W & 15);
 }

@@ -201,6 +201,7 @@ struct FoldArgs {
     void* xn_out;
     int64_t ldxn;
     int M, N, K;
+    bool ordinary = false;  // never a dependent launch
 };
 
 template <bool SCALED, int EPI>
@@ -211,7 +212,7 @@ int launch(const FoldArgs& a, cudaStream_t stream) {
     while (kw < max_kw && steps / (kw * 2) >= MIN_STEPS) kw *= 2;
     const int k_per_warp = ceil_div(steps, kw) * 32;
     const size_t smem = (size_t)kw * 16 * 8 * sizeof(float);
-    const bool dependent = skinny_dependent(ceil_div(a.N, 16));
+    const bool dependent = skinny_dependent(ceil_div(a.N, 16)) && !a.ordinary;
     cudaError_t e = launch_maybe_pdl(dependent, gemm_skinny_fold_kernel<SCALED, EPI>, dim3(ceil_div(a.N, 16)), dim3(kw * 32), smem, stream,
                                (const __nv_bfloat16*)a.X, a.ldx, a.stats_in, a.stats_count, a.stats_in_stride, a.eps,
                                (const __nv_bfloat16*)a.W, a.Y, (int)(a.y_dtype == GB_BF16), a.ldy, a.stats_out, a.stats_out_stride,
@@ -253,12 +254,15 @@ GB_API int gb_gemm_skinny_scaled(const void* X, int64_t ldx, float eps, const fl
 // Hres[M, N] += X[M, K] W^T (fp32 residual, in place); stats_out[row][c] = sum of squares of the 16
 // new values of the row in columns 16 c .. 16 c + 15; and, if next_w is given, xn_out[row][n] =
 // bf16(Hres[row][n] * next_w[n]), the next norm's output but for the row factor.
+// `ordinary`: launch as an ordinary kernel, never as a dependent one (for a product that follows a kernel
+// whose CTAs hold most of an SM's shared memory: see gb_gemm_scaled_algo).
 GB_API int gb_gemm_skinny_residual(const void* X, int64_t ldx, const void* W, float* Hres, int64_t ldh, float* stats_out,
                                    int64_t stats_out_stride, const float* next_w, void* xn_out, int64_t ldxn, int M, int N, int K,
-                                   cudaStream_t stream) {
+                                   int ordinary, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     const char* who = "gemm_skinny_residual";
     FoldArgs a = {X, ldx, nullptr, 0, 0, 0.f, W, Hres, GB_F32, ldh, stats_out, stats_out_stride, next_w, xn_out, ldxn, M, N, K};
+    a.ordinary = ordinary != 0;
     if (int rc = check_common(who, a)) return rc;
     if (ldh < N) GB_REFUSE("%s: row stride %lld of the residual is shorter than N = %d", who, (long long)ldh, N);
     if (!stats_out || stats_out_stride < ceil_div(N, 16)) GB_REFUSE("%s: the statistics buffer needs %d floats a row", who, ceil_div(N, 16));

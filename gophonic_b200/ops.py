@@ -287,12 +287,12 @@ def gemm_scaled_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_scaled(x: torch.Tensor, eps: float, stats: torch.Tensor, stats_count: int, w: torch.Tensor, out: torch.Tensor,
-                swiglu: bool = False) -> None:
+                swiglu: bool = False) -> str:
     """out[r] = rs[r] * (x[r] @ w^T) with rs[r] = 1 / sqrt(sum_r / K + eps), sum_r the sum of the
     ``stats_count`` partial sums stats[r, :stats_count]: the product of RMSNorm rows whose factor was
     left out when ``x = bf16(h * norm_weight)`` was made (by ``gemm_residual`` or ``embed_gather``).
     With ``swiglu``, ``w`` holds gate and up rows interleaved in blocks of eight and
-    out[M, N / 2] = silu(gate) * up."""
+    out[M, N / 2] = silu(gate) * up.  Returns the kernel's name."""
     _need(x, "prescaled rows", torch.bfloat16, 2, contiguous=False)
     _need(stats, "row statistics", torch.float32, 2)
     _need(w, "gemm w", torch.bfloat16, 2)
@@ -303,15 +303,16 @@ def gemm_scaled(x: torch.Tensor, eps: float, stats: torch.Tensor, stats_count: i
             or out.shape != (M, N // 2 if swiglu else N) or stats.shape[0] < M or not 0 < stats_count <= stats.shape[1]):
         raise KernelError(f"gemm_scaled: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
                           f"{stats_count} partial sums in {tuple(stats.shape)}")
-    if gemm_algo(M, N, K) == "skinny":   # the kernel ``gemm`` picks: fragment streaming, else tcgen05 decode
+    if _ALGO_NAMES[int(_lib.gb_gemm_scaled_algo(c_int(M), c_int(N), c_int(K), c_int(_sms())))] == "skinny":
         _check(_lib.gb_gemm_skinny_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
                                           c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
                                           c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream()))
-        return
+        return "skinny"
     splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sms())))
     _check(_lib.gb_gemm_tc5_decode_scaled(_ptr(x), c_int64(x.stride(0)), c_float(eps), _ptr(stats), c_int(stats_count),
                                           c_int64(stats.stride(0)), _ptr(w), _ptr(out), _code(out.dtype), c_int64(out.stride(0)),
                                           c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(splits), _stream()))
+    return "tc5_decode"
 
 
 def gemm_residual_accepts(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor) -> bool:
@@ -319,12 +320,14 @@ def gemm_residual_accepts(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor) -> 
 
 
 def gemm_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, stats: torch.Tensor,
-                  next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None) -> int:
+                  next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None, behind: str = "") -> int:
     """h += x @ w^T in place (``h`` float32: the residual stream; one float32 addition per element,
     as a separate add gives) and stats[row, c] = the sum of squares of the new values of the row
     in the c-th block of columns (16 wide up to 8 rows, 128 wide above).  With ``next_weight`` also next_x = bf16(h * next_weight), the rows
-    ``gemm_scaled`` takes.  ``stats`` needs ``fold_capacity(N)`` columns.  Returns the number of
-    partial sums a row."""
+    ``gemm_scaled`` takes.  ``stats`` needs ``fold_capacity(N)`` columns.  ``behind``: the kernel
+    that made ``x`` (what ``gemm_scaled`` returned), if the caller knows it; a few-row kernel behind
+    the tcgen05 decode kernel is launched as an ordinary kernel.  Returns the number of partial sums
+    a row."""
     _need(x, "gemm a", torch.bfloat16, 2, contiguous=False)
     _need(w, "gemm w", torch.bfloat16, 2)
     _need(h, "residual", torch.float32, 2, contiguous=False)
@@ -338,7 +341,7 @@ def gemm_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, stats: torc
     if gemm_algo(M, N, K) == "skinny":
         _check(_lib.gb_gemm_skinny_residual(_ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(h), c_int64(h.stride(0)), _ptr(stats),
                                             c_int64(stats.stride(0)), _ptr(next_weight), _ptr(next_x), c_int64(ldxn),
-                                            c_int(M), c_int(N), c_int(K), _stream()))
+                                            c_int(M), c_int(N), c_int(K), c_int(1 if behind == "tc5_decode" else 0), _stream()))
         return count
     splits = int(_lib.gb_gemm_tc5_decode_splits(c_int(M), c_int(N), c_int(K), c_int(_sms())))
     made = c_int(0)

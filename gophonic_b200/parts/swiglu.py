@@ -65,10 +65,10 @@ class SwiGLU(FeedForward):
         rows = h.shape[0]
         _, eps = norm.rms_fold()
         act = torch.empty((rows, self.spec.intermediate), dtype=self.rt.act_dtype, device=h.device)
-        ops.gemm_scaled(stats.prescaled, eps, stats.partials, stats.count, self.gate_up, act, swiglu=True)
+        made_by = ops.gemm_scaled(stats.prescaled, eps, stats.partials, stats.count, self.gate_up, act, swiglu=True)
         out_stats, out_rows = other_fold_buffers(batch, stats, self.spec.hidden)
         weight = fold_weight(next_norm, self.spec.hidden)
-        count = ops.gemm_residual(act, self.down, h, out_stats, weight, out_rows[:rows] if weight is not None else None)
+        count = ops.gemm_residual(act, self.down, h, out_stats, weight, out_rows[:rows] if weight is not None else None, behind=made_by)
         return RowStats(out_stats, count, out_rows[:rows] if weight is not None else None, next_norm if weight is not None else None)
 
     def _activation(self, x: torch.Tensor) -> torch.Tensor:
